@@ -1,0 +1,282 @@
+/*
+ * phobos_leaf.h — C ABI of the B200 leaf executor for phobos kernels.
+ *
+ * Every entry point is plain C (pointers, sizes, scalars by value) so that a
+ * Rust `extern "C"` block, cgo, JNI or ctypes can bind it unchanged.  Each
+ * declaration names the reference interface it stands in for, by file:line in
+ * the phobos repository.  All device pointers are CUDA device addresses owned
+ * by the caller; unless stated otherwise a call only ENQUEUES work on
+ * `stream` (a cudaStream_t passed as void*) and allocates nothing.
+ *
+ * Return value: 0 on success, a negative PhStatus otherwise; the message of
+ * the last failure on the calling thread is returned by phobos_last_error().
+ * There is no CPU fallback: without a usable sm_100 device every compute call
+ * fails with PH_ERR_DEVICE.
+ */
+#ifndef PHOBOS_LEAF_H_
+#define PHOBOS_LEAF_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define PH_API __attribute__((visibility("default")))
+#else
+#define PH_API
+#endif
+
+/* ---- status codes ------------------------------------------------------ */
+typedef enum PhStatus {
+  PH_OK = 0,
+  PH_ERR_INVALID = -1,    /* bad argument: rank, dtype, stride, alignment, shape mismatch */
+  PH_ERR_UNSUPPORTED = -2,/* a combination this executor has no kernel for */
+  PH_ERR_DEVICE = -3,     /* CUDA error, or no sm_100 device */
+  PH_ERR_WORKSPACE = -4,  /* caller workspace missing or too small */
+  PH_ERR_TIMEOUT = -5,    /* a bounded device-side wait gave up (see phobos_device_status) */
+  PH_ERR_IO = -6,         /* file:// storage error */
+  PH_ERR_PARSE = -7,      /* job file syntax */
+  PH_ERR_STATE = -8       /* executor: unknown tile, arena exhausted, dependency cycle */
+} PhStatus;
+
+/* ---- element types: order of phobos-cluster/src/tile.rs:33-41 ---------- */
+typedef enum PhDataType {
+  PH_F16 = 0, PH_F32 = 1, PH_F64 = 2, PH_I8 = 3, PH_I32 = 4, PH_I64 = 5, PH_BOOL = 6
+} PhDataType;
+
+/* bytes per element: phobos-cluster/src/tile.rs:43-52 */
+PH_API size_t phobos_dtype_bytes(int32_t dtype);
+
+/* ---- tensor descriptor -------------------------------------------------- *
+ * Stands in for the "exploded memref" the reference passes per tensor
+ * (alloc ptr, aligned ptr, offset, sizes[rank], strides[rank]; i32 or i64
+ * fields): phobos-bench/src/main.rs:290-327 and phobos-pod/src/engine.rs:588-601.
+ * `ptr` is the aligned pointer; `offset`, `sizes`, `strides` are in elements.
+ * Requirements (violations return PH_ERR_INVALID, never undefined behaviour):
+ * rank 1 or 2, inner stride 1, (ptr + offset) 16-byte aligned, row stride a
+ * multiple of 16 bytes — the reference assumes the same (SPEC.md:62).        */
+typedef struct PhTensor {
+  void *ptr;
+  int32_t dtype; /* PhDataType */
+  int32_t rank;
+  int64_t sizes[2];
+  int64_t strides[2];
+  int64_t offset;
+} PhTensor;
+
+/* ---- scalar argument ---------------------------------------------------- *
+ * phobos-cluster/src/isa.rs:7-11 (ScalarArg{pos,value}) with the value held
+ * as the little-endian bit pattern of ScalarValue::to_bits, tile.rs:75-83.   */
+typedef struct PhScalar {
+  uint32_t pos;   /* parameter position in the kernel signature */
+  int32_t dtype;  /* PH_F32, PH_F64, PH_I32, PH_I64, PH_BOOL */
+  uint64_t bits;
+} PhScalar;
+
+/* ---- which GEMM regime --------------------------------------------------- *
+ * The three `gemm` kernels of the reference share one signature and differ in
+ * element types and accumulator (examples/gemm_fp32.ph, gemm_fp16tc_fp32acc.ph,
+ * gemm_fp16.ph).                                                             */
+typedef enum PhGemmKind {
+  PH_GEMM_FP32 = 0,           /* f32 A,B,C; FFMA, no TF32            (gemm_fp32.ph:1-22) */
+  PH_GEMM_FP16TC_FP32ACC = 1, /* A,B f16 (or f32 rounded RN to f16 on the way in), C f32,
+                                 f32 accumulate                      (gemm_fp16tc_fp32acc.ph:1-23) */
+  PH_GEMM_FP16 = 2            /* f16 A,B,C, f16 accumulate, f32 epilogue (gemm_fp16.ph:1-23) */
+} PhGemmKind;
+
+/* ---- library / device ---------------------------------------------------- */
+PH_API const char *phobos_last_error(void);
+PH_API const char *phobos_version(void);
+
+typedef struct PhDeviceInfo {
+  int32_t device;
+  int32_t sm_count;
+  int32_t cc_major, cc_minor;
+  int32_t sm_clock_khz;       /* cudaDevAttrClockRate */
+  int64_t total_mem_bytes;
+  double fp32_peak_flops;     /* sm_count * 128 lanes * 2 * clock: the FP32 CUDA-core roofline */
+  char name[64];
+} PhDeviceInfo;
+PH_API int phobos_device_info(int device, PhDeviceInfo *out);
+
+/* Word written by a kernel whose bounded wait gave up (0 = none since the last
+ * reset).  Reads and clears the current device's status word; synchronises
+ * `stream` first. */
+PH_API int phobos_device_status(void *stream, uint32_t *status_out);
+
+/* ---- GEMM: C = alpha * A@B + beta * C ------------------------------------ *
+ * Replaces launch_gemm(func, grid, block, stream, a, b, c, M, N, K, alpha,
+ * beta, wide) of phobos-bench/src/main.rs:290-327 and the `gemm`/`matmul`
+ * COMPUTE of phobos-pod/src/engine.rs:542-653.  A[M,K], B[K,N], C[M,N],
+ * row-major.  C is read even when beta == 0 (the reference computes
+ * 0*C_old; phobos-lang/src/codegen/matmul.rs:393-402).  Non-blocking.
+ * `workspace` is only needed for PH_GEMM_FP16TC_FP32ACC with f32-stored A/B
+ * (rounded copies); size from phobos_gemm_workspace_bytes.                    */
+PH_API int phobos_gemm(const PhTensor *A, const PhTensor *B, const PhTensor *C, float alpha, float beta,
+                       int32_t kind, void *workspace, size_t workspace_bytes, void *stream);
+PH_API size_t phobos_gemm_workspace_bytes(int32_t kind, int32_t a_dtype, int64_t M, int64_t N, int64_t K);
+
+/* The init leaf of a partitioned matmul: C = beta * C, or C = 0 when there is
+ * no previous value (phobos-cluster/src/clustergen.rs:1276-1360; entry name
+ * `<kernel>_init`, clustergen.rs:1288).  The step leaf is phobos_gemm with
+ * beta = 1 (clustergen.rs:1363-1399).                                         */
+PH_API int phobos_matmul_init(const PhTensor *C, float beta, int32_t zero_fill, void *stream);
+
+/* ---- flash attention ------------------------------------------------------ *
+ * Replaces launch_flash(...) of phobos-bench/src/main.rs:334-371 and the
+ * `flash_attention` COMPUTE.  Q,O: [Nq,D]; K,V: [Nk,D] row-major
+ * (examples/flash_attention_fp16.ph:11-16).  `batch_heads` independent
+ * problems are run in one launch; problem h uses the descriptors advanced by
+ * h*Nq*D (Q,O) and h*Nk*D (K,V) elements.  Element type f16 (flash_fp16) or
+ * f32 (flash_fp32: operands rounded to f16 for the tensor cores as the
+ * reference does, phobos-lang/src/codegen/matmul.rs:1592-1597; needs
+ * workspace).  D must be 64 or 128.                                          */
+PH_API int phobos_flash_attention(const PhTensor *Q, const PhTensor *K, const PhTensor *V, const PhTensor *O,
+                                  float scale, int64_t batch_heads, void *workspace, size_t workspace_bytes,
+                                  void *stream);
+PH_API size_t phobos_flash_workspace_bytes(int32_t dtype, int64_t batch_heads, int64_t Nq, int64_t Nk, int64_t D);
+
+/* ---- launch by entry name -------------------------------------------------- *
+ * The COMPUTE operand model: Op::Compute{kernel, args, scalars, grid, cta}
+ * (phobos-cluster/src/isa.rs:38-44).  `entry` is the PTX entry name the
+ * reference would look up (= kernel name, phobos-lang/src/codegen/kernel.rs:90-93):
+ * "gemm", "matmul", "matmul_init", "flash_attention".  Tensors are in
+ * signature order; scalars carry their parameter position.  `grid` and `cta`
+ * describe the reference's own device tiling and are validated for presence
+ * only.  The GEMM regime follows from the element types unless `kind_hint`
+ * (a PhGemmKind, or -1) says otherwise.                                       */
+PH_API int phobos_launch(const char *entry, const PhTensor *tensors, int32_t n_tensors, const PhScalar *scalars,
+                         int32_t n_scalars, const uint32_t grid[3], const uint32_t cta[3], int32_t kind_hint,
+                         void *workspace, size_t workspace_bytes, void *stream);
+PH_API size_t phobos_launch_workspace_bytes(const char *entry, const PhTensor *tensors, int32_t n_tensors,
+                                            int32_t kind_hint);
+
+/* ---- input generator -------------------------------------------------------- *
+ * `phobos-tensor init --fill random --seed S` (phobos-cluster/src/bin/
+ * phobos-tensor.rs:55-72) = Lcg::unit_f32s (phobos-base/src/rng.rs:9-25):
+ * out[i] = scale * (f32(state_i >> 33) / 2^31 - 1), element i of the stream
+ * seeded with `seed`, starting at stream position `first`.  Host version
+ * writes host memory; device version fills device memory (f32, or f16 with
+ * the f32 value rounded RN-even) on `stream`.  `normal` != 0 draws N(0,1) by
+ * Box-Muller over stream pairs instead (no reference counterpart).            */
+PH_API int phobos_fill_random_host(float *out, uint64_t n, uint64_t seed, uint64_t first, float scale);
+PH_API int phobos_fill_random_device(void *out, int32_t dtype, uint64_t n, uint64_t seed, uint64_t first,
+                                     float scale, int32_t normal, void *stream);
+/* f32 -> f16 (RN-even) and back on the device; element counts. */
+PH_API int phobos_convert_f32_to_f16(const float *in, void *out_f16, uint64_t n, void *stream);
+PH_API int phobos_convert_f16_to_f32(const void *in_f16, float *out, uint64_t n, void *stream);
+
+/* ---- tile ids ---------------------------------------------------------------- *
+ * id = (tensor:12 << 52) | (version:16 << 36) | coord:36, phobos-cluster/src/tile.rs:5-30 */
+PH_API uint64_t phobos_tile_id(uint32_t tensor, uint32_t version, uint64_t coord);
+PH_API uint32_t phobos_tile_tensor(uint64_t id);
+PH_API uint32_t phobos_tile_version(uint64_t id);
+PH_API uint64_t phobos_tile_coord(uint64_t id);
+/* arena size class: phobos-pod/src/tile_store.rs:25-27 */
+PH_API uint64_t phobos_size_class(uint64_t bytes);
+
+/* ---- job file ------------------------------------------------------------------ *
+ * Grammar of phobos-sched/src/job.rs:5-88: `source = <path>`, `dim NAME = INT`,
+ * `tensor NAME = read|write|rmw DTYPE D0xD1 URI`, `scalar NAME = DTYPE VALUE`,
+ * `#` comments.  The source file is opened only to read the kernel's name.    */
+typedef struct PhJob PhJob;
+typedef enum PhAccessMode { PH_READ = 0, PH_WRITE = 1, PH_RMW = 2 } PhAccessMode; /* tile.rs:86-91 */
+PH_API PhJob *phobos_job_parse(const char *path);               /* NULL on error */
+PH_API PhJob *phobos_job_parse_text(const char *text, const char *origin, const char *source_text);
+PH_API void phobos_job_free(PhJob *job);
+PH_API const char *phobos_job_kernel_name(const PhJob *job);
+PH_API int32_t phobos_job_n_dims(const PhJob *job);
+PH_API const char *phobos_job_dim_name(const PhJob *job, int32_t i);
+PH_API int64_t phobos_job_dim_value(const PhJob *job, int32_t i);
+PH_API int32_t phobos_job_n_tensors(const PhJob *job);
+PH_API const char *phobos_job_tensor_name(const PhJob *job, int32_t i);
+PH_API int32_t phobos_job_tensor_dtype(const PhJob *job, int32_t i);
+PH_API int32_t phobos_job_tensor_mode(const PhJob *job, int32_t i);
+PH_API int32_t phobos_job_tensor_rank(const PhJob *job, int32_t i);
+PH_API int64_t phobos_job_tensor_dim(const PhJob *job, int32_t i, int32_t d);
+PH_API const char *phobos_job_tensor_uri(const PhJob *job, int32_t i);
+PH_API int32_t phobos_job_n_scalars(const PhJob *job);
+PH_API const char *phobos_job_scalar_name(const PhJob *job, int32_t i);
+PH_API int32_t phobos_job_scalar_dtype(const PhJob *job, int32_t i);
+PH_API uint64_t phobos_job_scalar_bits(const PhJob *job, int32_t i);
+
+/* ---- storage -------------------------------------------------------------------- *
+ * file:// tensors: headerless little-endian row-major blobs; a region LOAD
+ * gathers row spans into a contiguous tile and a region STORE scatters them
+ * back without truncating the file (phobos-cluster/src/storage.rs:9-79).  The
+ * reference is f32-only; `elem_bytes` generalises it.                          */
+typedef struct PhRegion {
+  int32_t rank;
+  uint64_t offset[2];
+  uint64_t shape[2];
+} PhRegion;
+PH_API int phobos_storage_path(const char *uri, char *out, size_t out_len);
+PH_API int phobos_storage_load(const char *uri, const uint64_t *tensor_shape, int32_t tensor_rank,
+                               const PhRegion *region, size_t elem_bytes, void *host_out);
+PH_API int phobos_storage_store(const char *uri, const uint64_t *tensor_shape, int32_t tensor_rank,
+                                const PhRegion *region, size_t elem_bytes, const void *host_in);
+
+/* ---- instruction executor ----------------------------------------------------------- *
+ * One executor per device: the pod's Engine (phobos-pod/src/engine.rs:121-232)
+ * without the network.  Instructions carry ids and dependency lists
+ * (isa.rs:52-63); an instruction is issued when all its deps have completed
+ * (engine.rs:282-323, 777-789).  Ops: isa.rs:24-50.                            */
+typedef enum PhOpCode { PH_OP_ALLOC = 0, PH_OP_LOAD = 1, PH_OP_FETCH = 2, PH_OP_COMPUTE = 3, PH_OP_STORE = 4,
+                        PH_OP_FREE = 5 } PhOpCode;
+
+typedef struct PhTileArg { uint64_t tile; int32_t mode; /* PhAccessMode */ } PhTileArg;
+
+typedef struct PhInstr {
+  uint64_t iid;
+  const uint64_t *deps;
+  int32_t n_deps;
+  int32_t op;                 /* PhOpCode */
+  uint64_t tile;              /* ALLOC, LOAD, FETCH, STORE, FREE */
+  int32_t data_type;          /* ALLOC */
+  int32_t shape_rank;         /* ALLOC */
+  uint64_t shape[2];          /* ALLOC */
+  uint32_t tensor;            /* LOAD/STORE: index into the tensor table (StorageRef::Tensor, isa.rs:19-22) */
+  PhRegion region;            /* LOAD/STORE */
+  uint32_t from_node;         /* FETCH: peer executor id */
+  uint32_t kernel;            /* COMPUTE: index into the kernel table */
+  const PhTileArg *args;      /* COMPUTE */
+  int32_t n_args;
+  const PhScalar *scalars;    /* COMPUTE */
+  int32_t n_scalars;
+  uint32_t grid[3], cta[3];   /* COMPUTE (validated, not used for tiling) */
+  uint32_t expected_serves;   /* FREE */
+} PhInstr;
+
+typedef struct PhTensorMeta { /* phobos-pod/src/engine.rs:22-27 */
+  const char *uri;
+  int32_t dtype;
+  int32_t rank;
+  uint64_t shape[2];
+  int32_t mode;
+} PhTensorMeta;
+
+typedef struct PhCompletion { uint64_t iid; uint32_t status; uint64_t elapsed_ns; } PhCompletion; /* engine.rs:70 */
+
+typedef struct PhExecutor PhExecutor;
+PH_API PhExecutor *phobos_executor_create(int32_t device, uint32_t node_id, uint64_t arena_bytes); /* NULL on error */
+PH_API void phobos_executor_destroy(PhExecutor *ex);
+PH_API int phobos_executor_set_tensors(PhExecutor *ex, const PhTensorMeta *tensors, int32_t n);   /* EngineMsg::SetTensors */
+PH_API int phobos_executor_set_kernel(PhExecutor *ex, uint32_t kernel_id, const char *entry, int32_t kind_hint); /* SetKernels */
+PH_API int phobos_executor_connect_peer(PhExecutor *ex, uint32_t node_id, PhExecutor *peer);      /* NodeAddrs/FetchLocs */
+PH_API int phobos_executor_issue(PhExecutor *ex, const PhInstr *instrs, int32_t n);               /* EngineMsg::Issue(Segment) */
+/* Runs the issue/poll loop until no instruction is pending or in flight.
+ * Returns 0, or the status of the first failed instruction (engine.rs:744-750). */
+PH_API int phobos_executor_run(PhExecutor *ex);
+PH_API int32_t phobos_executor_drain_completions(PhExecutor *ex, PhCompletion *out, int32_t cap);
+PH_API uint64_t phobos_executor_arena_used(const PhExecutor *ex);
+PH_API uint64_t phobos_executor_served_bytes(const PhExecutor *ex);  /* phobos-pod/src/server.rs:22 */
+/* Device address and residency of a tile (TileStore::addr/is_resident, tile_store.rs:134-140). */
+PH_API int phobos_executor_tile_addr(const PhExecutor *ex, uint64_t tile, void **addr_out, int32_t *resident_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PHOBOS_LEAF_H_ */

@@ -1,0 +1,45 @@
+// Internal launcher interface between api.cu and the kernel translation units.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace ph {
+
+// gemm_tc.cu — f16 operands on tcgen05 tensor cores.
+int launch_gemm_tc(const void* A, long long lda, const void* B, long long ldb, void* C, long long ldc, int M, int N,
+                   int K, float alpha, float beta, bool acc_f16, bool c_f16, int bn_override, int sm_count,
+                   uint32_t* status, cudaStream_t stream, const char** err);
+
+// tmap.cu — TMA descriptors (cuTensorMapEncodeTiled through the runtime's driver entry point).
+enum TmapType { TMAP_F16 = 0, TMAP_F32 = 1 };
+enum TmapSwizzle { TMAP_SWIZZLE_NONE = 0, TMAP_SWIZZLE_32B = 1, TMAP_SWIZZLE_64B = 2, TMAP_SWIZZLE_128B = 3 };
+// Row-major [rows, cols] tensor with row pitch ld_elems; box [box_rows, box_cols].
+// tmap_out points at 128 bytes, 64-byte aligned (a CUtensorMap).
+bool make_tmap_2d(void* tmap_out, const void* base, TmapType type, long long rows, long long cols,
+                  long long ld_elems, int box_rows, int box_cols, TmapSwizzle swizzle);
+// [batch, rows, cols] tensor: batch pitch in elements; box [1, box_rows, box_cols].
+bool make_tmap_3d(void* tmap_out, const void* base, TmapType type, long long batch, long long rows, long long cols,
+                  long long ld_elems, long long batch_pitch_elems, int box_rows, int box_cols, TmapSwizzle swizzle);
+
+// gemm_f32.cu — FFMA GEMM and the matmul_init leaf.
+int launch_gemm_f32(const float* A, long long lda, const float* B, long long ldb, float* C, long long ldc, int M,
+                    int N, int K, float alpha, float beta, uint32_t* status, cudaStream_t stream, const char** err);
+int launch_scale_f32(float* C, long long ldc, long long rows, long long cols, float beta, bool zero_fill,
+                     cudaStream_t stream, const char** err);
+
+// flash.cu — flash attention forward, f16 operands.
+// out_f32 != 0: O is f32 (flash_fp32), otherwise f16.
+int launch_flash_f16(const void* Q, const void* K, const void* V, void* O, int out_f32, long long batch_heads,
+                     int Nq, int Nk, int D, float scale, int sm_count, uint32_t* status, cudaStream_t stream,
+                     const char** err);
+
+// elementwise.cu — generator and conversions.
+int launch_fill_random(void* out, int dtype_is_f16, unsigned long long n, unsigned long long seed,
+                       unsigned long long first, float scale, int normal, cudaStream_t stream, const char** err);
+int launch_f32_to_f16(const float* in, void* out, unsigned long long n, cudaStream_t stream, const char** err);
+int launch_f16_to_f32(const void* in, float* out, unsigned long long n, cudaStream_t stream, const char** err);
+// Strided 2-D f32 -> contiguous f16 (rows x cols), used to stage f32-stored tensor-core operands.
+int launch_f32_to_f16_2d(const float* in, long long ld_in, void* out, long long rows, long long cols,
+                         cudaStream_t stream, const char** err);
+
+}  // namespace ph
