@@ -1,0 +1,546 @@
+#!/usr/bin/env python
+"""Benchmark of the phobos leaf kernels on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-suite]
+
+Prints ONE JSON line.  Metric: TFLOP/s under the reference's flop conventions
+(GEMM 2MNK + MN, phobos-bench/src/main.rs:591; flash 4*Nq*Nk*D per head, main.rs:1032).
+
+N = 1: the headline workload is gemm_fp16tc_fp32acc at M=N=K=4096 (f16 A/B, f32
+accumulate and C, alpha 1, beta 0); the other single-GPU configurations
+(gemm_fp32 4096^3, gemm_fp16 8192^3, flash_fp16 B4 H32 S4096 D128,
+matmul_cluster_fp32 16384^3 on one GPU) are measured the same way and reported
+under "suite".  N > 1: the partitioned matmul_cluster_fp32 16384^3 (2-D C
+partition, A/B panels exchanged over NVLink), strong scaling, launched one rank
+per GPU under torchrun.
+
+`--impl reference` times the reference's CPU arithmetic for the same workload (the
+oracle port of its f64 verifier math, all host threads) on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+NOMINAL_F16_TFLOPS = 2250.0
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu
+# captures summarised under profiles/; None where no capture exists yet.
+NCU_TRAFFIC_BYTES = {
+    "gemm_fp16tc_fp32acc": None,
+    "gemm_fp32": None,
+    "gemm_fp16": None,
+    "flash_fp16": None,
+    "matmul_cluster_fp32": None,
+}
+
+
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        d["_source"] = "measured"
+        return d
+    d = dict(FALLBACK_PEAKS)
+    d["_source"] = "fallback"
+    return d
+
+
+# ---------------------------------------------------------------------------------------------
+# clocks: sample nvidia-smi while the timed regions run
+# ---------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+
+        def reader():
+            for line in self.proc.stdout:
+                self.rows.append((time.time(), line.strip()))
+        self.thread = threading.Thread(target=reader, daemon=True)
+        self.thread.start()
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self, windows):
+        """windows: list of (t0, t1) wall-clock intervals during which timed kernels ran."""
+        sm, smax, reasons, power = [], [], set(), []
+        for t, line in self.rows:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 7:
+                continue
+            under_load = any(a - 0.05 <= t <= b + 0.15 for a, b in windows)
+            try:
+                clk, mx, pw = float(parts[0]), float(parts[1]), float(parts[2])
+            except ValueError:
+                continue
+            smax.append(mx)
+            if under_load:
+                sm.append(clk)
+                power.append(pw)
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                     parts[3:7]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        if not sm:  # timed regions shorter than the sampling period: fall back to every sample
+            for t, line in self.rows:
+                parts = [x.strip() for x in line.split(",")]
+                try:
+                    sm.append(float(parts[0]))
+                except (ValueError, IndexError):
+                    pass
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples_under_load": len(power),
+                "power_w_max": max(power) if power else None}
+
+
+# ---------------------------------------------------------------------------------------------
+# workloads
+# ---------------------------------------------------------------------------------------------
+def gemm_flops(M, N, K):
+    return 2.0 * M * N * K + M * N
+
+
+class Ctx:
+    def __init__(self, ph, torch, dev, steps, warmup):
+        self.ph, self.torch, self.dev, self.steps, self.warmup = ph, torch, dev, steps, warmup
+        self.windows = []
+
+    def time_steps(self, fn_step, steps=None, warmup=None, barrier=None):
+        """Runs warm-up steps, then times `steps` steps: total by one event pair around
+        the region (for `value`) and each launch by its own event pair (for the roofline)."""
+        torch = self.torch
+        steps = self.steps if steps is None else steps
+        warmup = self.warmup if warmup is None else warmup
+        for i in range(warmup):
+            fn_step(i)
+        torch.cuda.synchronize()
+        if barrier:
+            barrier()
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        t0 = torch.cuda.Event(enable_timing=True)
+        t1 = torch.cuda.Event(enable_timing=True)
+        w0 = time.time()
+        t0.record()
+        for i in range(steps):
+            evs[i][0].record()
+            fn_step(warmup + i)
+            evs[i][1].record()
+        t1.record()
+        torch.cuda.synchronize()
+        if barrier:
+            barrier()
+        self.windows.append((w0, time.time()))
+        total_ms = t0.elapsed_time(t1)
+        per = [a.elapsed_time(b) for a, b in evs]
+        return total_ms / steps, sum(per) / len(per), min(per)
+
+
+def pinned_like(torch, t):
+    h = torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=True)
+    h.copy_(t)
+    return h
+
+
+def bench_gemm(ctx: Ctx, name: str, M: int, N: int, K: int, alpha: float, beta: float, peaks, cpu_baseline=True,
+               e2e=True):
+    ph, torch, dev = ctx.ph, ctx.torch, ctx.dev
+    kind = {"gemm_fp32": ph.GEMM_FP32, "matmul_cluster_fp32": ph.GEMM_FP32,
+            "gemm_fp16tc_fp32acc": ph.GEMM_FP16TC_FP32ACC, "gemm_fp16": ph.GEMM_FP16}[name]
+    ab_dt = torch.float32 if kind == ph.GEMM_FP32 else torch.float16
+    c_dt = torch.float16 if kind == ph.GEMM_FP16 else torch.float32
+    scale = 0.5 if kind == ph.GEMM_FP16 else 1.0
+    set_bytes = (M * K + K * N) * (2 if ab_dt == torch.float16 else 4) + M * N * (2 if c_dt == torch.float16 else 4)
+    nsets = max(1, min(4, math.ceil(300e6 / set_bytes)))  # rotate input sets so the working set exceeds L2 (126 MB)
+    sets = []
+    for s in range(nsets):
+        A = torch.empty((M, K), dtype=ab_dt, device=dev)
+        B = torch.empty((K, N), dtype=ab_dt, device=dev)
+        C = torch.empty((M, N), dtype=c_dt, device=dev)
+        ph.fill_random(A, seed=1 + 10 * s, scale=scale)
+        ph.fill_random(B, seed=2 + 10 * s, scale=scale)
+        ph.fill_random(C, seed=3 + 10 * s, scale=scale)
+        sets.append((A, B, C))
+    # beta != 0 with |beta| > 1 would grow C over repeated steps: keep a pristine copy and restore outside timing
+    pristine = [s[2].clone() for s in sets] if beta != 0.0 else None
+
+    def step(i):
+        A, B, C = sets[i % nsets]
+        ph.gemm(A, B, C, alpha, beta, kind)
+
+    ms_total, ms_launch, ms_min = ctx.time_steps(step)
+    ph.device_status()
+    if pristine is not None:
+        for s, p0 in zip(sets, pristine):
+            s[2].copy_(p0)
+    flops = gemm_flops(M, N, K)
+    out = {"workload": name, "M": M, "N": N, "K": K, "alpha": alpha, "beta": beta,
+           "tflops": flops / (ms_total * 1e-3) / 1e12, "ms_per_step": ms_total, "ms_per_launch": ms_launch,
+           "ms_min": ms_min, "input_sets": nsets}
+    if kind == ph.GEMM_FP32:
+        info = ph.device_info(dev.index or 0)
+        peak = info.fp32_peak_flops / 1e12
+        out["roofline"] = {"bound": "fp32_ffma", "achieved": flops / (ms_launch * 1e-3) / 1e12, "peak": peak,
+                           "unit": "TFLOP/s", "frac": flops / (ms_launch * 1e-3) / 1e12 / peak,
+                           "peak_source": f"{info.sm_count} SMs x 128 lanes x 2 x {info.sm_clock_khz / 1e3:.0f} MHz",
+                           "traffic": NCU_TRAFFIC_BYTES.get(name)}
+    else:
+        peak = peaks["bf16_tflops"]
+        ach = flops / (ms_launch * 1e-3) / 1e12
+        out["roofline"] = {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
+                           "peak_source": f"of {peaks['_source']} (burst cuBLAS bf16)",
+                           "frac_of_nominal_2250": ach / NOMINAL_F16_TFLOPS, "traffic": NCU_TRAFFIC_BYTES.get(name)}
+    if e2e:
+        A, B, C = sets[0]
+        hA, hB, hC = pinned_like(torch, A), pinned_like(torch, B), pinned_like(torch, C)
+        hOut = torch.empty(C.shape, dtype=C.dtype, device="cpu", pin_memory=True)
+
+        def e2e_step(i):
+            A.copy_(hA, non_blocking=True)
+            B.copy_(hB, non_blocking=True)
+            C.copy_(hC, non_blocking=True)
+            ph.gemm(A, B, C, alpha, beta, kind)
+            hOut.copy_(C, non_blocking=True)
+
+        ms_e2e, _, _ = ctx.time_steps(e2e_step, steps=max(3, min(ctx.steps, 10)), warmup=3)
+        out["e2e"] = {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
+                      "h2d_bytes_per_step": hA.numel() * hA.element_size() + hB.numel() * hB.element_size()
+                      + hC.numel() * hC.element_size(),
+                      "d2h_bytes_per_step": hOut.numel() * hOut.element_size()}
+    if cpu_baseline:
+        out["cpu_baseline"] = cpu_gemm_baseline(name, M, N, K, alpha, beta)
+    del sets
+    torch.cuda.empty_cache()
+    return out
+
+
+def bench_flash(ctx: Ctx, BH: int, S: int, D: int, peaks, cpu_baseline=True, e2e=True):
+    ph, torch, dev = ctx.ph, ctx.torch, ctx.dev
+    scale = 1.0 / math.sqrt(D)
+    Q, K, V = (torch.empty((BH, S, D), dtype=torch.float16, device=dev) for _ in range(3))
+    for t, seed in ((Q, 4), (K, 5), (V, 6)):
+        ph.fill_random(t, seed=seed, normal=True)   # N(0,1): Box-Muller over the Lcg stream (no reference analogue)
+    O = torch.empty_like(Q)
+
+    def step(i):
+        ph.flash_attention(Q, K, V, O, scale)
+
+    ms_total, ms_launch, ms_min = ctx.time_steps(step)
+    ph.device_status()
+    flops = 4.0 * BH * S * S * D
+    ach = flops / (ms_launch * 1e-3) / 1e12
+    peak = peaks["bf16_tflops"]
+    out = {"workload": "flash_fp16", "batch_heads": BH, "seq_len": S, "head_dim": D,
+           "tflops": flops / (ms_total * 1e-3) / 1e12, "ms_per_step": ms_total, "ms_per_launch": ms_launch,
+           "ms_min": ms_min, "exp_per_s": BH * S * S / (ms_launch * 1e-3),
+           "roofline": {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
+                        "peak_source": f"of {peaks['_source']} (burst cuBLAS bf16)",
+                        "frac_of_nominal_2250": ach / NOMINAL_F16_TFLOPS, "traffic": NCU_TRAFFIC_BYTES.get("flash_fp16")}}
+    if e2e:
+        hQ, hK, hV = (pinned_like(torch, t) for t in (Q, K, V))
+        hO = torch.empty(O.shape, dtype=O.dtype, device="cpu", pin_memory=True)
+
+        def e2e_step(i):
+            Q.copy_(hQ, non_blocking=True)
+            K.copy_(hK, non_blocking=True)
+            V.copy_(hV, non_blocking=True)
+            ph.flash_attention(Q, K, V, O, scale)
+            hO.copy_(O, non_blocking=True)
+
+        ms_e2e, _, _ = ctx.time_steps(e2e_step, steps=max(3, min(ctx.steps, 10)), warmup=3)
+        nb = Q.numel() * 2
+        out["e2e"] = {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
+                      "h2d_bytes_per_step": 3 * nb, "d2h_bytes_per_step": nb}
+    if cpu_baseline:
+        out["cpu_baseline"] = cpu_flash_baseline(BH, S, D)
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU baseline: the oracle (port of the reference's f64 verifier arithmetic), bounded sample
+# ---------------------------------------------------------------------------------------------
+def cpu_gemm_baseline(name, M, N, K, alpha, beta, budget_flops=4e11):
+    import numpy as np
+    import oracle
+    rows_n = int(max(64, min(M, budget_flops / (2.0 * N * K))))
+    rows_n -= rows_n % 4
+    rows = np.arange(rows_n, dtype=np.uint64)
+    half = name in ("gemm_fp16tc_fp32acc", "gemm_fp16")
+    scale = 0.5 if name == "gemm_fp16" else 1.0
+    a = oracle.lcg_fill(1, rows_n * K, scale).reshape(rows_n, K)
+    b = oracle.lcg_fill(2, K * N, scale).reshape(K, N)
+    c = oracle.lcg_fill(3, rows_n * N, scale).reshape(rows_n, N)
+    if half:
+        a, b = oracle.fp16_round(a), oracle.fp16_round(b)
+    t0 = time.time()
+    oracle.gemm_rows(a, b, c, alpha, beta, rows=rows)
+    dt = time.time() - t0
+    fl = 2.0 * rows_n * N * K + rows_n * N
+    return {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": oracle.threads(), "kind": "port",
+            "sample": f"{rows_n} of {M} output rows x all {N} columns, K={K} (f64 accumulate, OpenMP); {dt:.2f} s"}
+
+
+def cpu_flash_baseline(BH, S, D, rows_n=256):
+    import numpy as np
+    import oracle
+    q = oracle.fp16_round(oracle.lcg_fill_normal(4, S * D)).reshape(S, D)
+    k = oracle.fp16_round(oracle.lcg_fill_normal(5, S * D)).reshape(S, D)
+    v = oracle.fp16_round(oracle.lcg_fill_normal(6, S * D)).reshape(S, D)
+    rows = np.arange(0, S, S // rows_n, dtype=np.uint64)[:rows_n]
+    t0 = time.time()
+    oracle.flash_rows(q, k, v, 1.0 / math.sqrt(D), rows=rows)
+    dt = time.time() - t0
+    fl = 4.0 * rows.size * S * D
+    return {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": oracle.threads(), "kind": "port",
+            "sample": f"{rows.size} of {BH * S} query rows of one head, all {S} keys (f64 online softmax, OpenMP); {dt:.2f} s"}
+
+
+# ---------------------------------------------------------------------------------------------
+# N > 1: partitioned matmul_cluster_fp32
+# ---------------------------------------------------------------------------------------------
+def bench_partitioned(ctx: Ctx, world: int, rank: int, MNK: int, alpha: float, beta: float):
+    import torch.distributed as dist
+    ph, torch, dev = ctx.ph, ctx.torch, ctx.dev
+    part = sys.modules[ph.__name__ + ".partition"]
+    kc = part.default_k_chunk(MNK, world)
+    plan = part.plan_partition(MNK, MNK, MNK, world, k_chunk=kc)
+    row_pg, col_pg = part.make_groups(plan, rank)
+    row0, mb, col0, nb = plan.c_block(rank)
+    ak0, aw = plan.a_shard_k(rank)
+    bk0, bh = plan.b_shard_k(rank)
+    # home shards, generated in place from the global Lcg streams (A seed 1, B seed 2, C seed 3)
+    a_rows = torch.empty((mb, aw), dtype=torch.float32, device=dev)
+    b_shard = torch.empty((bh, nb), dtype=torch.float32, device=dev)
+    c0 = torch.empty((mb, nb), dtype=torch.float32, device=dev)
+    fill_block(ph, a_rows, 1, row0, ak0, MNK)
+    fill_block(ph, b_shard, 2, bk0, col0, MNK)
+    fill_block(ph, c0, 3, row0, col0, MNK)
+    a_shard = a_rows.reshape(mb, aw // kc, kc).permute(1, 0, 2).contiguous()
+    del a_rows
+    c_block = c0.clone()
+    comm, comp = torch.cuda.Stream(), torch.cuda.Stream()
+    bufs = part.alloc_buffers(plan, a_shard, b_shard)
+    leaf_init, leaf_step = part.cuda_leaves()
+
+    def step(i):
+        part.run_partitioned(plan, rank, a_shard, b_shard, c_block, alpha, beta, leaf_init, leaf_step, row_pg, col_pg,
+                             comm_stream=comm, compute_stream=comp, buffers=bufs)
+        torch.cuda.current_stream().wait_stream(comp)
+        torch.cuda.current_stream().wait_stream(comm)
+
+    def reset():
+        c_block.copy_(c0)
+
+    def timed_step(i):
+        reset()
+        step(i)
+
+    # C is restored before every step; the restore (a device copy of the C block) is part of the step,
+    # as the reference's per-launch C reset is (phobos-bench/src/main.rs:267-279)
+    ms_total, ms_launch, ms_min = ctx.time_steps(timed_step, barrier=dist.barrier)
+    ph.device_status()
+    t = torch.tensor([ms_total], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    flops = gemm_flops(MNK, MNK, MNK)
+
+    # e2e: shards come from pinned host memory every step, the C block goes back
+    hA, hB, hC = pinned_like(torch, a_shard), pinned_like(torch, b_shard), pinned_like(torch, c0)
+    hOut = torch.empty(c0.shape, dtype=c0.dtype, device="cpu", pin_memory=True)
+
+    def e2e_step(i):
+        a_shard.copy_(hA, non_blocking=True)
+        b_shard.copy_(hB, non_blocking=True)
+        c_block.copy_(hC, non_blocking=True)
+        comp.wait_stream(torch.cuda.current_stream())
+        step(i)
+        hOut.copy_(c_block, non_blocking=True)
+
+    ms_e2e, _, _ = ctx.time_steps(e2e_step, steps=max(3, min(ctx.steps, 5)), warmup=3, barrier=dist.barrier)
+    t = torch.tensor([ms_e2e], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_e2e = float(t.item())
+    info = ph.device_info(dev.index or 0)
+    peak = info.fp32_peak_flops / 1e12 * world
+    ach = flops / (ms * 1e-3) / 1e12
+    out = {"workload": "matmul_cluster_fp32", "M": MNK, "N": MNK, "K": MNK, "alpha": alpha, "beta": beta,
+           "grid": f"{plan.pr}x{plan.pc}", "k_chunk": kc, "steps_per_rank": len(plan.steps),
+           "tflops": ach, "ms_per_step": ms,
+           "peer_bytes_per_step": plan.total_peer_bytes(), "peer_bytes_per_rank": plan.recv_bytes(rank),
+           "roofline": {"bound": "fp32_ffma", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
+                        "peak_source": f"{world} x {info.sm_count} SMs x 128 lanes x 2 x {info.sm_clock_khz / 1e3:.0f} MHz",
+                        "nvlink_floor_ms": plan.recv_bytes(rank) / 770e9 * 1e3, "traffic": None},
+           "e2e": {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
+                   "h2d_bytes_per_step": world * (hA.numel() + hB.numel() + hC.numel()) * 4,
+                   "d2h_bytes_per_step": world * hOut.numel() * 4},
+           "gpu_launches": (1 + len(plan.steps)) * ctx.steps * world}
+    return out
+
+
+def fill_block(ph, t, seed, row0, col0, pitch):
+    """Fills t[r, c] with element (row0 + r) * pitch + col0 + c of the Lcg stream `seed`."""
+    ph.fill_random_block(t, seed=seed, first=row0 * pitch + col0, stream_pitch=pitch)
+
+
+# ---------------------------------------------------------------------------------------------
+def run_reference(args, world, rank):
+    """The reference's CPU arithmetic for the workload, on the host cores (rank 0 only)."""
+    if rank != 0:
+        return
+    import __graft_entry__ as entry  # noqa: F401  (oracle only; the product library is not loaded)
+    import oracle
+    oracle.build()
+    if args.gpus == 1:
+        name, M, N, K, alpha, beta = "gemm_fp16tc_fp32acc", 4096, 4096, 4096, 1.0, 0.0
+    else:
+        name, M, N, K, alpha, beta = "matmul_cluster_fp32", 16384, 16384, 16384, 0.125, 1.5
+    vals = []
+    sample = ""
+    for i in range(args.warmup + args.steps):
+        r = cpu_gemm_baseline(name, M, N, K, alpha, beta, budget_flops=1.5e11)
+        if i >= args.warmup:
+            vals.append(r["value"])
+        sample = r["sample"]
+    v = sum(vals) / len(vals)
+    fl_full = gemm_flops(M, N, K)
+    line = {"impl": "reference", "metric": "GEMM & flash-attn TFLOP/s at 1/2/4/8 B200 and % of dtype roofline",
+            "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": fl_full / (v * 1e12) * 1e3, "higher_is_better": True,
+            "scaling": "weak" if args.gpus == 1 else "strong", "vs_baseline": None, "dtype": "f64",
+            "data": "synthetic (seeded Lcg, phobos-base/src/rng.rs)",
+            "config": {"workload": name, "M": M, "N": N, "K": K, "alpha": alpha, "beta": beta,
+                       "note": "ms_per_step extrapolates the sampled rows to the full problem"},
+            "cpu_baseline": {"value": v, "unit": "TFLOP/s", "cores": oracle.threads(), "kind": "port",
+                             "sample": sample},
+            "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-suite", action="store_true", help="headline workload only")
+    ap.add_argument("--only", default=None, help="run one suite workload as the headline (profiling)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, world, rank)
+        return
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    import __graft_entry__ as entry
+    ph = entry.load_package()
+    ph.lib()  # no fallback: raises if the CUDA library is missing
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (the leaf kernels have no CPU path)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    peaks = load_peaks()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ctx = Ctx(ph, torch, dev, args.steps, args.warmup)
+    metric = "GEMM & flash-attn TFLOP/s at 1/2/4/8 B200 and % of dtype roofline"
+    cpu = not args.no_cpu
+
+    if world > 1 or args.gpus > 1:
+        import torch.distributed as dist
+        if world != args.gpus:
+            raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})")
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+        res = bench_partitioned(ctx, world, rank, 16384, 0.125, 1.5)
+        if rank == 0:
+            res["cpu_baseline"] = None
+            line = {"metric": metric, "value": res["tflops"], "unit": "TFLOP/s", "n_gpus": world,
+                    "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["ms_per_step"],
+                    "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+                    "data": "synthetic (seeded Lcg streams of phobos-base/src/rng.rs, generated on the device)",
+                    "config": {"workload": "matmul_cluster_fp32", "M": 16384, "N": 16384, "K": 16384, "alpha": 0.125,
+                               "beta": 1.5, "parallelism": f"2-D C partition {res['grid']}, K chunks of {res['k_chunk']}"
+                               " broadcast over NVLink (NCCL) one step ahead of the step leaf",
+                               "l2": "operands (1 GiB each) exceed L2"},
+                    "roofline": res["roofline"], "e2e": {k: v for k, v in res["e2e"].items()},
+                    "gpu_launches": res["gpu_launches"], "peer_bytes_per_step": res["peer_bytes_per_step"]}
+        dist.barrier()
+        sampler.stop()
+        if rank == 0:
+            line["clocks"] = sampler.summary(ctx.windows)
+            print(json.dumps(line), flush=True)
+        dist.destroy_process_group()
+        return
+
+    suite = {}
+    runners = {
+        "gemm_fp16tc_fp32acc": lambda: bench_gemm(ctx, "gemm_fp16tc_fp32acc", 4096, 4096, 4096, 1.0, 0.0, peaks, cpu),
+        "gemm_fp32": lambda: bench_gemm(ctx, "gemm_fp32", 4096, 4096, 4096, 0.125, 1.5, peaks, cpu),
+        "gemm_fp16": lambda: bench_gemm(ctx, "gemm_fp16", 8192, 8192, 8192, 1.0, 1.0, peaks, cpu),
+        "flash_fp16": lambda: bench_flash(ctx, 128, 4096, 128, peaks, cpu),
+        "matmul_cluster_fp32": lambda: bench_gemm(ctx, "matmul_cluster_fp32", 16384, 16384, 16384, 0.125, 1.5, peaks,
+                                                  cpu_baseline=False, e2e=False),
+    }
+    head_name = args.only or "gemm_fp16tc_fp32acc"
+    head = runners[head_name]()
+    if not args.no_suite and not args.only:
+        for name, fn in runners.items():
+            if name != head_name:
+                steps_save = ctx.steps
+                if name == "matmul_cluster_fp32":
+                    ctx.steps = min(ctx.steps, 5)
+                suite[name] = fn()
+                ctx.steps = steps_save
+    sampler.stop()
+    line = {"metric": metric, "value": head["tflops"], "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": {"gemm_fp32": "f32", "matmul_cluster_fp32": "f32", "gemm_fp16": "f16"}.get(head_name, "f16 x f16 -> f32"),
+            "data": "synthetic (seeded Lcg streams of phobos-base/src/rng.rs, generated on the device)",
+            "config": {"workload": head_name, **{k: head[k] for k in head if k in ("M", "N", "K", "alpha", "beta", "batch_heads", "seq_len", "head_dim")},
+                       "l2": f"{head.get('input_sets', 1)} rotating input sets, working set larger than L2"},
+            "roofline": head["roofline"], "cpu_baseline": head.get("cpu_baseline"), "e2e": head.get("e2e"),
+            "gpu_launches": args.steps, "clocks": sampler.summary(ctx.windows), "suite": suite}
+    print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

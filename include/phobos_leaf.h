@@ -165,6 +165,11 @@ PH_API size_t phobos_launch_workspace_bytes(const char *entry, const PhTensor *t
 PH_API int phobos_fill_random_host(float *out, uint64_t n, uint64_t seed, uint64_t first, float scale);
 PH_API int phobos_fill_random_device(void *out, int32_t dtype, uint64_t n, uint64_t seed, uint64_t first,
                                      float scale, int32_t normal, void *stream);
+/* A rows x cols block of a larger row-major tensor whose element (i, j) is
+ * stream element i*stream_pitch + j: out[r*ld_out + c] takes stream element
+ * first + r*stream_pitch + c (a region of the tensor `phobos-tensor init` writes). */
+PH_API int phobos_fill_random_block(void *out, int32_t dtype, uint64_t rows, uint64_t cols, uint64_t ld_out,
+                                    uint64_t seed, uint64_t first, uint64_t stream_pitch, float scale, void *stream);
 /* f32 -> f16 (RN-even) and back on the device; element counts. */
 PH_API int phobos_convert_f32_to_f16(const float *in, void *out_f16, uint64_t n, void *stream);
 PH_API int phobos_convert_f16_to_f32(const void *in_f16, float *out, uint64_t n, void *stream);

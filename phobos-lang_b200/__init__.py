@@ -105,6 +105,7 @@ def lib() -> ctypes.CDLL:
             "phobos_launch_workspace_bytes": (sz, [c.c_char_p, TP, i32, i32]),
             "phobos_fill_random_host": (c.c_int, [c.POINTER(f32), u64, u64, u64, f32]),
             "phobos_fill_random_device": (c.c_int, [vp, i32, u64, u64, u64, f32, i32, vp]),
+            "phobos_fill_random_block": (c.c_int, [vp, i32, u64, u64, u64, u64, u64, u64, f32, vp]),
             "phobos_convert_f32_to_f16": (c.c_int, [vp, vp, u64, vp]),
             "phobos_convert_f16_to_f32": (c.c_int, [vp, vp, u64, vp]),
             "phobos_tile_id": (u64, [u32, u32, u64]),
@@ -296,6 +297,15 @@ def fill_random(out, seed: int, first: int = 0, scale: float = 1.0, normal: bool
         raise PhobosError(PH_ERR_INVALID, "fill_random needs a contiguous tensor")
     check(lib().phobos_fill_random_device(out.data_ptr(), _torch_dtype_code(out), out.numel(), seed, first, scale,
                                           int(normal), _stream_ptr(stream)))
+
+
+def fill_random_block(out, seed: int, first: int, stream_pitch: int, scale: float = 1.0, stream=None) -> None:
+    """Fill a 2-D CUDA tensor (inner stride 1) with a block of a larger seeded tensor: element (r, c)
+    takes stream element first + r*stream_pitch + c."""
+    if out.dim() != 2 or out.stride(1) != 1:
+        raise PhobosError(PH_ERR_INVALID, "fill_random_block needs a rank-2 tensor with inner stride 1")
+    check(lib().phobos_fill_random_block(out.data_ptr(), _torch_dtype_code(out), out.shape[0], out.shape[1],
+                                         out.stride(0), seed, first, stream_pitch, scale, _stream_ptr(stream)))
 
 
 def fill_random_host(n: int, seed: int, first: int = 0, scale: float = 1.0):

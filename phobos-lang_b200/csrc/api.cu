@@ -403,6 +403,22 @@ int phobos_fill_random_device(void* out, int32_t dtype, uint64_t n, uint64_t see
   return map_launch_rc(rc, "fill_random", err);
 }
 
+int phobos_fill_random_block(void* out, int32_t dtype, uint64_t rows, uint64_t cols, uint64_t ld_out, uint64_t seed,
+                             uint64_t first, uint64_t stream_pitch, float scale, void* stream) {
+  clear_error();
+  if (!out && rows * cols) return fail(PH_ERR_INVALID, "null output");
+  if (dtype != PH_F16 && dtype != PH_F32) return fail(PH_ERR_UNSUPPORTED, "fill: element type %d", dtype);
+  if (ld_out < cols) return fail(PH_ERR_INVALID, "fill: output pitch %llu smaller than %llu columns",
+                                 (unsigned long long)ld_out, (unsigned long long)cols);
+  DeviceState* ds;
+  int rc;
+  if ((rc = device_state(&ds))) return rc;
+  const char* err = "";
+  rc = launch_fill_random_block(out, dtype == PH_F16, rows, cols, ld_out, seed, first, stream_pitch, scale,
+                                static_cast<cudaStream_t>(stream), &err);
+  return map_launch_rc(rc, "fill_random_block", err);
+}
+
 int phobos_convert_f32_to_f16(const float* in, void* out, uint64_t n, void* stream) {
   clear_error();
   if ((!in || !out) && n) return fail(PH_ERR_INVALID, "null pointer");

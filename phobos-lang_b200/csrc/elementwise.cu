@@ -60,6 +60,20 @@ __global__ void fill_uniform_kernel(T* out, unsigned long long n, unsigned long 
   for (unsigned long long i = lo; i < hi; i++) put<T>(out, i, __fmul_rn(scale, lcg_unit(s)));
 }
 
+// Block variant: row r of the output takes stream elements first + r*pitch + [0, cols).
+template <typename T>
+__global__ void fill_block_kernel(T* out, unsigned long long rows, unsigned long long cols, unsigned long long ld_out,
+                                  unsigned long long seed, unsigned long long first, unsigned long long pitch,
+                                  float scale) {
+  const unsigned long long runs_per_row = (cols + PER_THREAD - 1) / PER_THREAD;
+  const unsigned long long t = blockIdx.x * static_cast<unsigned long long>(blockDim.x) + threadIdx.x;
+  if (t >= rows * runs_per_row) return;
+  const unsigned long long r = t / runs_per_row, lo = (t - r * runs_per_row) * PER_THREAD;
+  const unsigned long long hi = lo + PER_THREAD < cols ? lo + PER_THREAD : cols;
+  unsigned long long s = lcg_skip(seed, first + r * pitch + lo);
+  for (unsigned long long c = lo; c < hi; c++) put<T>(out, r * ld_out + c, __fmul_rn(scale, lcg_unit(s)));
+}
+
 // N(0,1): Box-Muller over stream pairs (2p, 2p+1): u1 = ((s>>33)+1)/2^31 in
 // (0,1], u2 = (s>>33)/2^31 in [0,1).  Element 2p is r cos(2 pi u2), 2p+1 is
 // r sin(2 pi u2).  `first` must be even.
@@ -168,6 +182,21 @@ int launch_fill_random(void* out, int dtype_is_f16, unsigned long long n, unsign
     else
       fill_uniform_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<float*>(out), n, seed, first, scale);
   }
+  return check(err);
+}
+
+int launch_fill_random_block(void* out, int dtype_is_f16, unsigned long long rows, unsigned long long cols,
+                             unsigned long long ld_out, unsigned long long seed, unsigned long long first,
+                             unsigned long long stream_pitch, float scale, cudaStream_t stream, const char** err) {
+  if (rows == 0 || cols == 0) return 0;
+  const unsigned long long threads = rows * ((cols + PER_THREAD - 1) / PER_THREAD);
+  const unsigned blocks = static_cast<unsigned>((threads + 255) / 256);
+  if (dtype_is_f16)
+    fill_block_kernel<__half><<<blocks, 256, 0, stream>>>(static_cast<__half*>(out), rows, cols, ld_out, seed, first,
+                                                         stream_pitch, scale);
+  else
+    fill_block_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<float*>(out), rows, cols, ld_out, seed, first,
+                                                        stream_pitch, scale);
   return check(err);
 }
 

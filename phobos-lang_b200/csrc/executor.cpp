@@ -25,6 +25,7 @@
 #include <cstring>
 #include <deque>
 #include <map>
+#include <mutex>
 #include <string>
 #include <unordered_map>
 #include <vector>
@@ -139,6 +140,8 @@ struct PhExecutor {
   uint64_t served_bytes = 0;
   int first_failure = 0;
   std::string first_failure_msg;
+  // guards the tile table and counters against a peer's FETCH running on another host thread
+  std::mutex mu;
 };
 
 namespace {
@@ -297,6 +300,9 @@ bool do_fetch(PhExecutor* ex, uint64_t iid, const Node& n) {
     return true;
   }
   PhExecutor* peer = pe->second;
+  // try_lock: two executors fetching from each other must not wait on each other's lock
+  std::unique_lock<std::mutex> peer_lock(peer->mu, std::try_to_lock);
+  if (peer != ex && !peer_lock.owns_lock()) return false;
   auto src = peer->tiles.find(n.in.tile);
   if (src == peer->tiles.end() || !src->second.resident) return false;  // served once resident (engine.rs:698-705)
   auto dst = ex->tiles.find(n.in.tile);
@@ -319,6 +325,12 @@ bool do_fetch(PhExecutor* ex, uint64_t iid, const Node& n) {
                                       reinterpret_cast<void*>(src->second.slab.addr), peer->device, bytes, s);
   if (e != cudaSuccess) {
     fail_instr(ex, iid, PH_ERR_DEVICE, std::string("FETCH: ") + cudaGetErrorString(e));
+    return true;
+  }
+  // the serve counts once the data has left the source tile (the reference
+  // serves a finished device-to-host copy): the home may FREE it right after
+  if (cudaStreamSynchronize(s) != cudaSuccess) {
+    fail_instr(ex, iid, PH_ERR_DEVICE, "FETCH: copy did not complete");
     return true;
   }
   src->second.serves++;
@@ -558,6 +570,7 @@ int phobos_executor_run(PhExecutor* ex) {
   DeviceGuard g(ex->device);
   int idle_rounds = 0;
   while (true) {
+    std::unique_lock<std::mutex> self_lock(ex->mu);
     bool progressed = poll_inflight(ex);
     while (!ex->ready.empty()) {
       uint64_t iid = ex->ready.front();
@@ -600,6 +613,7 @@ int phobos_executor_run(PhExecutor* ex) {
         ex->first_failure_msg = "stalled waiting for a peer (FETCH source never became resident, or FREE never served)";
         break;
       }
+      self_lock.unlock();
       struct timespec ts = {0, 100000};  // 100 us, as the reference's idle sleep (engine.rs:225-230)
       nanosleep(&ts, nullptr);
     } else {

@@ -36,6 +36,9 @@ int launch_flash_f16(const void* Q, const void* K, const void* V, void* O, int o
 // elementwise.cu — generator and conversions.
 int launch_fill_random(void* out, int dtype_is_f16, unsigned long long n, unsigned long long seed,
                        unsigned long long first, float scale, int normal, cudaStream_t stream, const char** err);
+int launch_fill_random_block(void* out, int dtype_is_f16, unsigned long long rows, unsigned long long cols,
+                             unsigned long long ld_out, unsigned long long seed, unsigned long long first,
+                             unsigned long long stream_pitch, float scale, cudaStream_t stream, const char** err);
 int launch_f32_to_f16(const float* in, void* out, unsigned long long n, cudaStream_t stream, const char** err);
 int launch_f16_to_f32(const void* in, float* out, unsigned long long n, cudaStream_t stream, const char** err);
 // Strided 2-D f32 -> contiguous f16 (rows x cols), used to stage f32-stored tensor-core operands.
