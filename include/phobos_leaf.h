@@ -139,6 +139,15 @@ PH_API int phobos_flash_attention(const PhTensor *Q, const PhTensor *K, const Ph
                                   void *stream);
 PH_API size_t phobos_flash_workspace_bytes(int32_t dtype, int64_t batch_heads, int64_t Nq, int64_t Nk, int64_t D);
 
+/* Diagnostic (no reference counterpart; the reference only has `--autotune` pins
+ * "for ncu profiling", phobos-bench/src/main.rs:35-36): while a device buffer of
+ * at least 2048 64-bit words is set for the current device, CTA (0,0) of every
+ * flash launch records clock64 stamps of its pipeline phases in it, laid out
+ * [role: softmax tile 0, softmax tile 1, MMA issuer, TMA producer][key block < 64]
+ * [slot < 8].  NULL switches tracing off.  Only libraries built with
+ * -DPH_FLASH_TRACE carry the stamps; others return PH_ERR_UNSUPPORTED.        */
+PH_API int phobos_flash_trace(uint64_t *device_buf, uint64_t n_words);
+
 /* ---- launch by entry name -------------------------------------------------- *
  * The COMPUTE operand model: Op::Compute{kernel, args, scalars, grid, cta}
  * (phobos-cluster/src/isa.rs:38-44).  `entry` is the PTX entry name the

@@ -101,6 +101,7 @@ def lib() -> ctypes.CDLL:
             "phobos_matmul_init": (c.c_int, [TP, f32, i32, vp]),
             "phobos_flash_attention": (c.c_int, [TP, TP, TP, TP, f32, i64, vp, sz, vp]),
             "phobos_flash_workspace_bytes": (sz, [i32, i64, i64, i64, i64]),
+            "phobos_flash_trace": (c.c_int, [vp, u64]),
             "phobos_launch": (c.c_int, [c.c_char_p, TP, i32, SP, i32, c.POINTER(u32), c.POINTER(u32), i32, vp, sz, vp]),
             "phobos_launch_workspace_bytes": (sz, [c.c_char_p, TP, i32, i32]),
             "phobos_fill_random_host": (c.c_int, [c.POINTER(f32), u64, u64, u64, f32]),

@@ -125,6 +125,23 @@ static int gemm_bn_override() {
   return s ? atoi(s) : 0;
 }
 
+// Tensor-core GEMM dispatch: CTA pairs once the problem spans at least one
+// 256-row pair tile per pair of SMs' worth of work, the 1-CTA kernel below that.
+// PHOBOS_GEMM_MODE=1 / 2 forces one of them (experiments only).
+static int launch_tc(const void* A, long long lda, const void* B, long long ldb, void* C, long long ldc, int M, int N,
+                     int K, float alpha, float beta, bool acc_f16, bool c_f16, int sm_count, uint32_t* status,
+                     cudaStream_t stream, const char** err) {
+  const char* mode = getenv("PHOBOS_GEMM_MODE");
+  bool pair = static_cast<long long>((M + 255) / 256) * ((N + 255) / 256) >= sm_count / 4 && M >= 256 && N >= 128;
+  if (mode && mode[0] == '1') pair = false;
+  if (mode && mode[0] == '2') pair = true;
+  if (pair)
+    return launch_gemm_tc_pair(A, lda, B, ldb, C, ldc, M, N, K, alpha, beta, acc_f16, c_f16, gemm_bn_override(),
+                               sm_count, status, stream, err);
+  return launch_gemm_tc(A, lda, B, ldb, C, ldc, M, N, K, alpha, beta, acc_f16, c_f16, gemm_bn_override(), sm_count,
+                        status, stream, err);
+}
+
 }  // namespace ph
 
 using namespace ph;
@@ -235,15 +252,15 @@ int phobos_gemm(const PhTensor* A, const PhTensor* B, const PhTensor* C, float a
         if ((K * 2) % 16 != 0 || (N * 2) % 16 != 0)
           return fail(PH_ERR_INVALID, "gemm_fp16tc_fp32acc: K and N must be multiples of 8");
       }
-      rc = launch_gemm_tc(a16, lda, b16, ldb, c.base, c.ld, (int)M, (int)N, (int)K, alpha, beta, false, false,
-                          gemm_bn_override(), ds->sm_count, ds->status, stream, &err);
+      rc = launch_tc(a16, lda, b16, ldb, c.base, c.ld, (int)M, (int)N, (int)K, alpha, beta, false, false,
+                     ds->sm_count, ds->status, stream, &err);
       return map_launch_rc(rc, "gemm_fp16tc_fp32acc", err);
     }
     case PH_GEMM_FP16: {
       if (a.dtype != PH_F16 || b.dtype != PH_F16 || c.dtype != PH_F16)
         return fail(PH_ERR_INVALID, "gemm_fp16 takes f16 A, B and C");
-      rc = launch_gemm_tc(a.base, a.ld, b.base, b.ld, c.base, c.ld, (int)M, (int)N, (int)K, alpha, beta, true, true,
-                          gemm_bn_override(), ds->sm_count, ds->status, stream, &err);
+      rc = launch_tc(a.base, a.ld, b.base, b.ld, c.base, c.ld, (int)M, (int)N, (int)K, alpha, beta, true, true,
+                     ds->sm_count, ds->status, stream, &err);
       return map_launch_rc(rc, "gemm_fp16", err);
     }
     default:
@@ -312,6 +329,18 @@ int phobos_flash_attention(const PhTensor* Q, const PhTensor* K, const PhTensor*
   rc = launch_flash_f16(q16, k16, v16, o.base, q.dtype == PH_F32 ? 1 : 0, batch_heads, (int)Nq, (int)Nk, (int)D, scale,
                         ds->sm_count, ds->status, stream, &err);
   return map_launch_rc(rc, "flash_attention", err);
+}
+
+int phobos_flash_trace(uint64_t* device_buf, uint64_t n_words) {
+  clear_error();
+#ifndef PH_FLASH_TRACE
+  if (device_buf != nullptr)
+    return fail(PH_ERR_UNSUPPORTED, "this build has no flash trace stamps (compile with -DPH_FLASH_TRACE)");
+#endif
+  int rc = set_flash_trace(reinterpret_cast<unsigned long long*>(device_buf), n_words);
+  if (rc == -1) return fail(PH_ERR_INVALID, "flash trace buffer needs at least 2048 64-bit words");
+  if (rc) return fail(PH_ERR_DEVICE, "no current device");
+  return PH_OK;
 }
 
 // ---- launch by entry name ---------------------------------------------------------------

@@ -91,11 +91,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // records `site`) when the wait ran out or another thread already reported a
 // failure; the caller must then stop issuing work and fall through to teardown.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t site, const WaitCtx& ctx) {
-  if (mbar_try_wait(bar, parity)) return true;
+  // fast path: polls without touching the (slow to read) global timer
+#ifndef PH_WAIT_FAST_POLLS
+#define PH_WAIT_FAST_POLLS 512
+#endif
+#pragma unroll 1
+  for (int i = 0; i < PH_WAIT_FAST_POLLS; i++)
+    if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 0x3FF) == 0) {
+    if ((++spins & 0xFF) == 0) {
       if (*ctx.abort_flag != 0) return false;
       if (globaltimer_ns() - t0 > PH_WAIT_NS) {
         *ctx.abort_flag = site;
@@ -106,6 +112,22 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
   }
   return true;
 }
+
+// Whole-warp wait: lane 0 polls, the result is broadcast, so a waiting warp
+// costs one polling thread instead of 32.  Every lane of the warp must call it.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, uint32_t site, const WaitCtx& ctx) {
+  uint32_t ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, site, ctx) ? 1u : 0u;
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  return ok != 0;
+}
+
+// Waits executed by a whole warp ahead of warp-collective TMEM accesses.
+#ifndef PH_WAIT_ALL_LANES
+#define PH_WARP_WAIT(bar, parity, site, ctx) mbar_wait_warp(bar, parity, site, ctx)
+#else
+#define PH_WARP_WAIT(bar, parity, site, ctx) __all_sync(0xffffffffu, mbar_wait(bar, parity, site, ctx))
+#endif
 
 // ---- TMA ----------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tmap(const void* tmap) {
@@ -254,6 +276,70 @@ __device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// ---- CTA pairs (cluster of 2, tcgen05 cta_group::2) -------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Shared-window address of `local_addr` as seen in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Tiled 2-D load into this CTA's shared memory whose completion bytes are
+// counted on an mbarrier that may live in the peer CTA of the pair.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const void* tmap, uint32_t mbar_cluster_addr,
+                                                 int32_t x, int32_t y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], "
+      "[%2];" ::"r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(tmap)), "r"(mbar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// D (+)= A * B over a CTA pair: M = 256 rows split over the two CTAs' tensor
+// memory, each CTA's shared memory holding its 128 rows of A and its half of
+// B's N columns.  Issued by ONE thread of the leader CTA.
+__device__ __forceinline__ void umma_f16_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive (once all MMAs issued so far are done) on the barrier at this
+// shared-memory offset in every CTA of `cta_mask`.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t cta_mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+          smem_u32(bar)),
+      "h"(cta_mask)
+      : "memory");
+}
 
 // Named barrier among a subset of warps (id 1..15; 0 is __syncthreads).
 __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t nthreads) {

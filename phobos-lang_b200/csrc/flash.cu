@@ -17,14 +17,31 @@
 //
 // One CTA owns 256 query rows of one (batch, head): two 128-row tiles that
 // ping-pong so that the tensor core works on one tile while the other tile's
-// softmax runs.  Warp roles (320 threads):
+// softmax runs.  Warp roles (384 threads; the two softmax warpgroups raise their
+// register budget with setmaxnreg, the third warpgroup lowers its own):
 //   warps 0-3  softmax + correction + epilogue of query tile 0 (one row per thread)
 //   warps 4-7  the same for query tile 1
-//   warp 8     TMA producer: Q once, then K and V blocks of 128 keys, 2 stages each
+//   warp 8     TMA producer: Q once, then K and V blocks of 128 keys through one
+//              ring of five slots (a block takes thousands of clocks to land while
+//              the MMAs saturate shared memory, so the ring runs two blocks ahead)
 //   warp 9     tcgen05.mma issuer: S_i = Q_i K^T into tensor memory, then
-//              O_i += P_i V with P_i read from tensor memory (it overwrites S_i)
+//              O_i += P_i V with P_i read from tensor memory (it overwrites S_i).
+//              One issuer for both tiles: two issuer warps (one per tile) were
+//              measured 20% slower, the tensor pipe does not interleave two
+//              instruction streams well
+//   warps 10-11 idle (they complete the third warpgroup)
 // Tensor memory columns: S0 | S1 | O0 | O1.
+//
+// Exponentials: a 128x128 score tile needs 16384 exp2; the MUFU unit delivers 16
+// per clock per SM, i.e. 1024 clocks per tile, exactly what the tensor core needs
+// for the tile's two MMAs.  EMU of every 8 column pairs are therefore evaluated
+// on the FMA pipes instead: 2^x = 2^n * p(f), n = round(x), f = x - n in
+// [-0.5, 0.5], p a cubic with relative error 7.5e-5 (P is rounded to f16, eps
+// 4.9e-4, right after).  The scale/subtract, the polynomial and the row sums use
+// packed f32x2 instructions to halve their issue slots.
 #include <cuda.h>
+
+#include <cstdlib>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -34,7 +51,7 @@ namespace {
 
 constexpr int QT = 128;        // query rows per tile
 constexpr int KB = 128;        // keys per block
-constexpr int FL_THREADS = 320;
+constexpr int FL_THREADS = 384;
 constexpr float RESCALE_TAU = 8.0f;          // log2 units
 constexpr float M_INIT = -65504.0f * 1.4426950408889634f;  // the .ph's -65504 in log2 units
 
@@ -44,7 +61,8 @@ struct FCfg {
   static constexpr int QTILE_BYTES = QT * D * 2;
   static constexpr int KV_BYTES = KB * D * 2;
   static constexpr int HALF_BYTES = 128 * 128;        // one [128 rows x 64 f16] box
-  static constexpr int SMEM_BYTES = 2 * QTILE_BYTES + 4 * KV_BYTES + 1024 + 256;
+  static constexpr int RING = 5;                      // K/V blocks in flight (shared ring)
+  static constexpr int SMEM_BYTES = 2 * QTILE_BYTES + RING * KV_BYTES + 1024 + 256;
   static constexpr int TMEM_COLS = 512;
   static constexpr int S_COL0 = 0;                    // S_i at i*128
   static constexpr int O_COL0 = 256;                  // O_i at 256 + i*D
@@ -57,7 +75,16 @@ struct FlashParams {
   int negate_q;       // scale < 0: negate Q inside the MMA instead
   void* O;            // [BH][Nq][D]
   uint32_t* status;
+  unsigned long long* trace;  // optional: clock stamps of CTA (0,0), see phobos_flash_trace
 };
+
+constexpr int TRACE_MAX_J = 64, TRACE_SLOTS = 8;
+__device__ __forceinline__ void stamp(unsigned long long* buf, int role, int j, int slot) {
+#ifdef PH_FLASH_TRACE
+  if (buf != nullptr && j < TRACE_MAX_J) buf[(role * TRACE_MAX_J + j) * TRACE_SLOTS + slot] = clock64();
+#endif
+}
+unsigned long long* g_trace_buf[64] = {};
 
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
@@ -70,26 +97,66 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
   return r;
 }
 
-template <int D, bool OUT_F32>
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "add.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// 2^x for a pair on the FMA pipes (x <= ~8; clamped below at -126).
+__device__ __forceinline__ float2 exp2_poly2(float2 x) {
+  constexpr float MAGIC = 12582912.0f;  // 1.5 * 2^23: adding it rounds to the nearest integer
+  x.x = fmaxf(x.x, -126.0f);
+  x.y = fmaxf(x.y, -126.0f);
+  const float2 t = fadd2(x, make_float2(MAGIC, MAGIC));
+  const float2 n = fadd2(t, make_float2(-MAGIC, -MAGIC));
+  const float2 f = fadd2(x, make_float2(-n.x, -n.y));
+  float2 q = ffma2(make_float2(0.055171653628349304f, 0.055171653628349304f), f,
+                   make_float2(0.2426111251115799f, 0.2426111251115799f));
+  q = ffma2(q, f, make_float2(0.6932609677314758f, 0.6932609677314758f));
+  q = ffma2(q, f, make_float2(0.9999280571937561f, 0.9999280571937561f));
+  // the integer part sits in the low bits of t: shifting it into the exponent field adds n to the exponent
+  float2 r;
+  r.x = __int_as_float(__float_as_int(q.x) + (__float_as_int(t.x) << 23));
+  r.y = __int_as_float(__float_as_int(q.y) + (__float_as_int(t.y) << 23));
+  return r;
+}
+
+template <int D, bool OUT_F32, int EMU>
 __global__ void __launch_bounds__(FL_THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, FlashParams p) {
   using C_ = FCfg<D>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // K and V blocks share one ring of RING slots, filled in consumption order
+  // K0 V0 K1 V1 ...: item n (K_j = 2j, V_j = 2j+1) lives in slot n % RING.
+  constexpr int RING = C_::RING;
   uint8_t* sQ = smem;                                  // 2 tiles
-  uint8_t* sK = smem + 2 * C_::QTILE_BYTES;            // 2 stages
-  uint8_t* sV = sK + 2 * C_::KV_BYTES;                 // 2 stages
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + 2 * C_::KV_BYTES);
-  uint64_t* q_full = bars;          // 1
-  uint64_t* k_full = bars + 1;      // 2
-  uint64_t* k_empty = bars + 3;     // 2
-  uint64_t* v_full = bars + 5;      // 2
-  uint64_t* v_empty = bars + 7;     // 2
-  uint64_t* s_full = bars + 9;      // 2 (per query tile)
-  uint64_t* p_full = bars + 11;     // 2
-  uint64_t* o_done = bars + 13;     // 2
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  uint8_t* sKV = smem + 2 * C_::QTILE_BYTES;           // RING slots
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + RING * C_::KV_BYTES);
+  uint64_t* q_full = bars;                 // 1
+  uint64_t* kv_full = bars + 1;            // RING
+  uint64_t* kv_empty = bars + 1 + RING;    // RING
+  uint64_t* s_full = bars + 1 + 2 * RING;  // 2 (per query tile)
+  uint64_t* p_full = s_full + 2;           // 2
+  uint64_t* o_done = s_full + 4;           // 2
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 6);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -101,11 +168,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
+    for (int s = 0; s < RING; s++) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
     for (int s = 0; s < 2; s++) {
-      mbar_init(&k_full[s], 1);
-      mbar_init(&k_empty[s], 1);
-      mbar_init(&v_full[s], 1);
-      mbar_init(&v_empty[s], 1);
       mbar_init(&s_full[s], 1);
       mbar_init(&p_full[s], 128);
       mbar_init(&o_done[s], 1);
@@ -125,6 +192,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
+  if (warp >= 8) {
+  // the third warpgroup hands registers to the softmax warpgroups
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 120;");
   if (warp == 8) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
@@ -132,17 +202,23 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       for (int i = 0; i < 2; i++)
         for (int h = 0; h < C_::HALVES; h++)
           tma_load_3d(sQ + i * C_::QTILE_BYTES + h * C_::HALF_BYTES, &tmQ, q_full, h * 64, q_row0 + i * QT, head);
-      for (int j = 0; j < nkb; j++) {
-        const int st = j & 1;
-        const uint32_t par = ((j >> 1) & 1) ^ 1;
-        if (!mbar_wait(&k_empty[st], par, SITE_FLASH_LOAD, wctx)) break;
-        mbar_arrive_expect_tx(&k_full[st], C_::KV_BYTES);
+      unsigned long long* tb = (blockIdx.x == 0 && blockIdx.y == 0) ? p.trace : nullptr;
+      int slot = 0;
+      uint32_t par = 1;  // parity that a never-used slot's `empty` barrier passes
+      for (int n = 0; n < 2 * nkb; n++) {
+        const int j = n >> 1;
+        const bool is_v = (n & 1) != 0;
+        stamp(tb, 3, j, is_v ? 2 : 0);
+        if (!mbar_wait(&kv_empty[slot], par, SITE_FLASH_LOAD, wctx)) break;
+        stamp(tb, 3, j, is_v ? 3 : 1);
+        mbar_arrive_expect_tx(&kv_full[slot], C_::KV_BYTES);
         for (int h = 0; h < C_::HALVES; h++)
-          tma_load_3d(sK + st * C_::KV_BYTES + h * C_::HALF_BYTES, &tmK, &k_full[st], h * 64, j * KB, head);
-        if (!mbar_wait(&v_empty[st], par, SITE_FLASH_LOAD, wctx)) break;
-        mbar_arrive_expect_tx(&v_full[st], C_::KV_BYTES);
-        for (int h = 0; h < C_::HALVES; h++)
-          tma_load_3d(sV + st * C_::KV_BYTES + h * C_::HALF_BYTES, &tmV, &v_full[st], h * 64, j * KB, head);
+          tma_load_3d(sKV + slot * C_::KV_BYTES + h * C_::HALF_BYTES, is_v ? &tmV : &tmK, &kv_full[slot], h * 64,
+                      j * KB, head);
+        if (++slot == RING) {
+          slot = 0;
+          par ^= 1;
+        }
       }
     }
   } else if (warp == 9) {
@@ -152,66 +228,92 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const uint32_t idesc_s = umma_idesc_f16(QT, KB, true, false, false) | (p.negate_q ? (1u << 13) : 0u);
       // O += P V : M=128, N=D, A (P) from tensor memory, B (V) N-major
       constexpr uint32_t idesc_o = umma_idesc_f16(QT, D, true, false, true);
-      auto issue_s = [&](int i, int kstage) {
-        const uint32_t qa = smem_u32(sQ + i * C_::QTILE_BYTES);
-        const uint32_t ka = smem_u32(sK + kstage * C_::KV_BYTES);
+      // descriptors are built once; an operand elsewhere is the base descriptor plus
+      // its byte offset >> 4 in the address field
+      const uint64_t q_desc0 = umma_smem_desc(smem_u32(sQ), 16, 1024);                    // K-major
+      const uint64_t k_desc0 = umma_smem_desc(smem_u32(sKV), 16, 1024);                   // K-major
+      const uint64_t v_desc0 = umma_smem_desc(smem_u32(sKV), C_::HALF_BYTES, 1024);       // N-major
+      auto issue_s = [&](int i, int slot) {
+        const uint64_t qd = q_desc0 + static_cast<uint64_t>(i * (C_::QTILE_BYTES >> 4));
+        const uint64_t kd = k_desc0 + static_cast<uint64_t>(slot * (C_::KV_BYTES >> 4));
         const uint32_t d = tmem_base + C_::S_COL0 + i * 128;
 #pragma unroll
         for (int kk = 0; kk < D / 16; kk++) {
-          const uint32_t off = (kk >> 2) * C_::HALF_BYTES + (kk & 3) * 32;
-          umma_f16_ss(d, umma_smem_desc(qa + off, 16, 1024), umma_smem_desc(ka + off, 16, 1024), idesc_s,
-                      kk != 0 ? 1u : 0u);
+          const uint64_t off = static_cast<uint64_t>(((kk >> 2) * C_::HALF_BYTES + (kk & 3) * 32) >> 4);
+          umma_f16_ss(d, qd + off, kd + off, idesc_s, kk != 0 ? 1u : 0u);
         }
       };
-      auto issue_pv = [&](int i, int vstage, bool accumulate) {
-        const uint32_t va = smem_u32(sV + vstage * C_::KV_BYTES);
+      auto issue_pv = [&](int i, int slot, bool accumulate) {
+        const uint64_t vd = v_desc0 + static_cast<uint64_t>(slot * (C_::KV_BYTES >> 4));
         const uint32_t d = tmem_base + C_::O_COL0 + i * D;
         const uint32_t pa = tmem_base + C_::S_COL0 + i * 128;  // P overwrote S, 2 f16 per column
 #pragma unroll
         for (int kk = 0; kk < KB / 16; kk++) {
-          // V block: [128 keys][64 d] per half; 8-key atoms 1024 B apart, halves HALF_BYTES apart
-          umma_f16_ts(d, pa + kk * 8, umma_smem_desc(va + kk * 2048, C_::HALF_BYTES, 1024), idesc_o,
+          // V block: [128 keys][64 d] per half; 8-key atoms 1024 B apart, halves HALF_BYTES apart;
+          // a step of 16 keys is 2048 B
+          umma_f16_ts(d, pa + kk * 8, vd + static_cast<uint64_t>(kk * (2048 >> 4)), idesc_o,
                       (accumulate || kk != 0) ? 1u : 0u);
         }
       };
-      bool ok = mbar_wait(q_full, 0, SITE_FLASH_MMA, wctx) && mbar_wait(&k_full[0], 0, SITE_FLASH_MMA, wctx);
+      // ring cursor, advanced once per item in consumption order K0 V0 K1 V1 ...
+      int cur = 0;
+      uint32_t cpar = 0;
+      auto advance = [&]() {
+        if (++cur == RING) {
+          cur = 0;
+          cpar ^= 1;
+        }
+      };
+      bool ok = mbar_wait(q_full, 0, SITE_FLASH_MMA, wctx) && mbar_wait(&kv_full[cur], cpar, SITE_FLASH_MMA, wctx);
       if (ok) {
         tc_fence_after_sync();
-        issue_s(0, 0);
+        issue_s(0, cur);
         umma_commit(&s_full[0]);
-        issue_s(1, 0);
+        issue_s(1, cur);
         umma_commit(&s_full[1]);
-        umma_commit(&k_empty[0]);
+        umma_commit(&kv_empty[cur]);
+        advance();
       }
+      unsigned long long* tb = (blockIdx.x == 0 && blockIdx.y == 0) ? p.trace : nullptr;
       for (int j = 0; j < nkb && ok; j++) {
-        const int st = j & 1;
-        if (!mbar_wait(&v_full[st], (j >> 1) & 1, SITE_FLASH_MMA, wctx)) break;
+        stamp(tb, 2, j, 0);
+        const int vs = cur;
+        if (!mbar_wait(&kv_full[vs], cpar, SITE_FLASH_MMA, wctx)) break;
+        advance();
+        const int ks = cur;
+        const uint32_t kpar = cpar;
+        const bool more = j + 1 < nkb;
+        if (more) advance();
         for (int i = 0; i < 2; i++) {
+          stamp(tb, 2, j, 1 + 3 * i);
           if (!mbar_wait(&p_full[i], j & 1, SITE_FLASH_MMA, wctx)) {
             ok = false;
             break;
           }
+          stamp(tb, 2, j, 2 + 3 * i);
           tc_fence_after_sync();
-          issue_pv(i, st, j > 0);
-          if (i == 1) umma_commit(&v_empty[st]);
-          if (j + 1 < nkb) {
-            const int ns = (j + 1) & 1;
-            if (i == 0 && !mbar_wait(&k_full[ns], ((j + 1) >> 1) & 1, SITE_FLASH_MMA, wctx)) {
+          issue_pv(i, vs, j > 0);
+          if (i == 1) umma_commit(&kv_empty[vs]);
+          if (more) {
+            if (i == 0 && !mbar_wait(&kv_full[ks], kpar, SITE_FLASH_MMA, wctx)) {
               ok = false;
               break;
             }
             tc_fence_after_sync();
-            issue_s(i, ns);
+            issue_s(i, ks);
             umma_commit(&s_full[i]);
-            if (i == 1) umma_commit(&k_empty[ns]);
+            if (i == 1) umma_commit(&kv_empty[ks]);
           } else {
             umma_commit(&o_done[i]);
           }
+          stamp(tb, 2, j, 3 + 3 * i);
         }
       }
     }
+  }
   } else {
     // ------------------------------ softmax / correction / epilogue ---------------
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 192;");
     const int i = warp >> 2;       // query tile
     const int q = warp & 3;        // TMEM lane quarter
     const int row_in_tile = q * 32 + lane;
@@ -223,9 +325,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     float m2 = M_INIT, l = 0.0f;
     bool ok = true;
 
+    unsigned long long* tb = (blockIdx.x == 0 && blockIdx.y == 0 && q == 0 && lane == 0) ? p.trace : nullptr;
     for (int j = 0; j < nkb; j++) {
+      stamp(tb, i, j, 0);
       // the vote keeps the warp together: the TMEM loads below are warp-collective
-      if (!__all_sync(0xffffffffu, mbar_wait(&s_full[i], j & 1, SITE_FLASH_SOFTMAX, wctx))) {
+      if (!PH_WARP_WAIT(&s_full[i], j & 1, SITE_FLASH_SOFTMAX, wctx)) {
         ok = false;
         break;
       }
@@ -233,7 +337,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       uint32_t sr[4][32];
 #pragma unroll
       for (int cc = 0; cc < 4; cc++) tmem_ld_32x32b_x32(s_addr + cc * 32, sr[cc]);
+      stamp(tb, i, j, 1);
       tmem_ld_wait();
+      stamp(tb, i, j, 2);
       const int valid = p.Nk - j * KB;  // keys of this block that exist
       if (valid < KB) {
 #pragma unroll
@@ -244,11 +350,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-      for (int e = 0; e < 32; e++) {
-        mx0 = fmaxf(mx0, __uint_as_float(sr[0][e]));
-        mx1 = fmaxf(mx1, __uint_as_float(sr[1][e]));
-        mx2 = fmaxf(mx2, __uint_as_float(sr[2][e]));
-        mx3 = fmaxf(mx3, __uint_as_float(sr[3][e]));
+      for (int e = 0; e < 32; e += 2) {
+        mx0 = max3(mx0, __uint_as_float(sr[0][e]), __uint_as_float(sr[0][e + 1]));
+        mx1 = max3(mx1, __uint_as_float(sr[1][e]), __uint_as_float(sr[1][e + 1]));
+        mx2 = max3(mx2, __uint_as_float(sr[2][e]), __uint_as_float(sr[2][e + 1]));
+        mx3 = max3(mx3, __uint_as_float(sr[3][e]), __uint_as_float(sr[3][e + 1]));
       }
       const float mnew = fmaxf(m2, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * c);
       if (j == 0) {
@@ -273,38 +379,43 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           if (need) m2 = mnew;
         }
       }
-      const float neg_m = -m2;
-      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+      stamp(tb, i, j, 3);
+      const float2 c2 = make_float2(c, c), neg_m2 = make_float2(-m2, -m2);
+      float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
       uint32_t pk[2][32];
 #pragma unroll
       for (int cc = 0; cc < 4; cc++) {
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
-          float p0 = ex2_approx(fmaf(__uint_as_float(sr[cc][e]), c, neg_m));
-          float p1 = ex2_approx(fmaf(__uint_as_float(sr[cc][e + 1]), c, neg_m));
-          if (valid < KB) {  // keys past the end contribute nothing
-            if (cc * 32 + e >= valid) p0 = 0.0f;
-            if (cc * 32 + e + 1 >= valid) p1 = 0.0f;
-          }
-          if ((e & 2) == 0) {
-            l0 += p0;
-            l1 += p1;
+          const float2 x = ffma2(make_float2(__uint_as_float(sr[cc][e]), __uint_as_float(sr[cc][e + 1])), c2, neg_m2);
+          float2 pr;
+          if (((e >> 1) & 7) < EMU) {
+            pr = exp2_poly2(x);
           } else {
-            l2 += p0;
-            l3 += p1;
+            pr.x = ex2_approx(x.x);
+            pr.y = ex2_approx(x.y);
           }
-          pk[cc >> 1][(cc & 1) * 16 + (e >> 1)] = pack_f16x2(p0, p1);
+          if (valid < KB) {  // keys past the end contribute nothing
+            if (cc * 32 + e >= valid) pr.x = 0.0f;
+            if (cc * 32 + e + 1 >= valid) pr.y = 0.0f;
+          }
+          if ((e & 2) == 0) la = fadd2(la, pr);
+          else lb = fadd2(lb, pr);
+          pk[cc >> 1][(cc & 1) * 16 + (e >> 1)] = pack_f16x2(pr.x, pr.y);
         }
       }
+      const float l0 = la.x, l1 = la.y, l2 = lb.x, l3 = lb.y;
       l += (l0 + l1) + (l2 + l3);
+      stamp(tb, i, j, 4);
       tmem_st_32x32b_x32(s_addr, pk[0]);
       tmem_st_32x32b_x32(s_addr + 32, pk[1]);
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(&p_full[i]);
+      stamp(tb, i, j, 5);
     }
 
-    if (ok && __all_sync(0xffffffffu, mbar_wait(&o_done[i], 0, SITE_FLASH_EPI, wctx))) {
+    if (ok && PH_WARP_WAIT(&o_done[i], 0, SITE_FLASH_EPI, wctx)) {
       tc_fence_after_sync();
       const float inv_l = 1.0f / l;
       const bool row_ok = row < p.Nq;
@@ -354,11 +465,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (warp == 9) tmem_dealloc(tmem_base, C_::TMEM_COLS);
 }
 
-template <int D, bool OUT_F32>
+template <int D, bool OUT_F32, int EMU>
 cudaError_t launch_d(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const FlashParams& p,
                      long long batch_heads, cudaStream_t stream) {
   using C_ = FCfg<D>;
-  auto kern = flash_fwd_kernel<D, OUT_F32>;
+  auto kern = flash_fwd_kernel<D, OUT_F32, EMU>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::SMEM_BYTES);
   if (e != cudaSuccess) return e;
   dim3 grid((p.Nq + 2 * QT - 1) / (2 * QT), static_cast<unsigned>(batch_heads));
@@ -367,6 +478,19 @@ cudaError_t launch_d(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUten
 }
 
 }  // namespace
+
+// Diagnostic: while a buffer is set for the current device, CTA (0,0) of every
+// flash launch writes clock64 stamps of its softmax and MMA phases into it
+// ([role 0..3][key block < 64][slot < 8] 64-bit words).  nullptr switches it off.
+// The stamps are compiled in only with -DPH_FLASH_TRACE (they cost the MMA issuer
+// thread about 4% otherwise).
+int set_flash_trace(unsigned long long* device_buf, unsigned long long words) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -3;
+  if (device_buf != nullptr && words < 4ull * TRACE_MAX_J * TRACE_SLOTS) return -1;
+  g_trace_buf[dev] = device_buf;
+  return 0;
+}
 
 int launch_flash_f16(const void* Q, const void* K, const void* V, void* O, int out_f32, long long batch_heads,
                      int Nq, int Nk, int D, float scale, int sm_count, uint32_t* status, cudaStream_t stream,
@@ -396,13 +520,26 @@ int launch_flash_f16(const void* Q, const void* K, const void* V, void* O, int o
   p.negate_q = scale < 0.0f ? 1 : 0;
   p.O = O;
   p.status = status;
+  {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    p.trace = (dev >= 0 && dev < 64) ? g_trace_buf[dev] : nullptr;
+  }
+  // column pairs per 8 evaluated by the polynomial; PHOBOS_FLASH_EMU overrides it (experiments only)
+  int emu = 0;
+  if (const char* ev = getenv("PHOBOS_FLASH_EMU")) emu = atoi(ev);
   cudaError_t e;
-  if (D == 128)
-    e = out_f32 ? launch_d<128, true>(tmQ, tmK, tmV, p, batch_heads, stream)
-                : launch_d<128, false>(tmQ, tmK, tmV, p, batch_heads, stream);
-  else
-    e = out_f32 ? launch_d<64, true>(tmQ, tmK, tmV, p, batch_heads, stream)
-                : launch_d<64, false>(tmQ, tmK, tmV, p, batch_heads, stream);
+  if (D == 128 && !out_f32) {
+    e = emu == 2 ? launch_d<128, false, 2>(tmQ, tmK, tmV, p, batch_heads, stream)
+        : emu == 4 ? launch_d<128, false, 4>(tmQ, tmK, tmV, p, batch_heads, stream)
+        : emu == 3 ? launch_d<128, false, 3>(tmQ, tmK, tmV, p, batch_heads, stream)
+                   : launch_d<128, false, 0>(tmQ, tmK, tmV, p, batch_heads, stream);
+  } else if (D == 128) {
+    e = launch_d<128, true, 0>(tmQ, tmK, tmV, p, batch_heads, stream);
+  } else {
+    e = out_f32 ? launch_d<64, true, 0>(tmQ, tmK, tmV, p, batch_heads, stream)
+                : launch_d<64, false, 0>(tmQ, tmK, tmV, p, batch_heads, stream);
+  }
   if (e != cudaSuccess) {
     *err = cudaGetErrorString(e);
     return -3;

@@ -10,11 +10,15 @@
 // to a sequential f32 fma chain.
 //
 // Structure: CTA tile 128x128, K step 16, 256 threads, 8x8 outputs per thread in
-// registers.  A [128 x 16] and B [16 x 128] tiles are staged by TMA into a
-// 4-deep ring of shared-memory stages (one elected thread issues, mbarriers
-// signal arrival); fragments are read with 128-bit shared loads.  The A tile is
-// stored 64B-swizzled so that the four rows a warp reads in one instruction land
-// in different banks.  Two CTAs are resident per SM.
+// registers.  A [128 x 16] and B [16 x 128] tiles are staged by TMA into a ring
+// of shared-memory stages; a `full` mbarrier per stage signals arrival and an
+// `empty` mbarrier (one arrival per warp) lets the refill proceed without a
+// CTA-wide barrier, so warps drift apart by up to a stage.  Fragments are read
+// with 128-bit shared loads; the A tile is stored 64B-swizzled so that the four
+// rows a warp reads in one instruction land in different banks.  The
+// multiply-adds are issued as packed fma.rn.f32x2 (two independent IEEE fmas per
+// instruction): the math is unchanged while the instruction count halves, which
+// moves the limit from the issue slots to the FMA pipe.  Two CTAs per SM.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -40,12 +44,28 @@ struct F32Params {
   uint32_t* status;
 };
 
+// acc (+)= a * b on both 32-bit halves: two fma.rn.f32 in one instruction.
+__device__ __forceinline__ void ffma2(unsigned long long& acc, unsigned long long a, unsigned long long b) {
+  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(a), "l"(b));
+}
+__device__ __forceinline__ unsigned long long dup2(float x) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %1};" : "=l"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ float2 unpack2(unsigned long long v) {
+  float2 r;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(r.x), "=f"(r.y) : "l"(v));
+  return r;
+}
+
 __global__ void __launch_bounds__(THREADS, 2)
 gemm_f32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, F32Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
-  volatile uint32_t* abort_flag = reinterpret_cast<uint32_t*>(full + STAGES);
+  uint64_t* empty = full + STAGES;
+  volatile uint32_t* abort_flag = reinterpret_cast<uint32_t*>(empty + STAGES);
   const WaitCtx wctx{abort_flag, p.status};
 
   // tile of this CTA: bands of 8 row-blocks for L2 reuse
@@ -70,7 +90,10 @@ gemm_f32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   const int tx = lane & 7;   // 0..7 : cols  wcol + tx*4 + 32*j + (0..3)
 
   if (tid == 0) {
-    for (int s = 0; s < STAGES; s++) mbar_init(&full[s], 1);
+    for (int s = 0; s < STAGES; s++) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], THREADS / 32);
+    }
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tmA);
@@ -88,50 +111,61 @@ gemm_f32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     for (int s = 0; s < STAGES && s < num_kb; s++) issue(s, s);
   }
 
-  float acc[8][8];
+  // acc[i][jp]: row wrow + ty + 4*i, column pair jp (columns 2*jp, 2*jp+1 of the thread's 8)
+  unsigned long long acc[8][4];
 #pragma unroll
   for (int i = 0; i < 8; i++)
 #pragma unroll
-    for (int j = 0; j < 8; j++) acc[i][j] = 0.0f;
+    for (int jp = 0; jp < 4; jp++) acc[i][jp] = 0ull;  // two +0.0f
 
-  // Per-row swizzled offsets inside an A tile: row r lives at r*64 B and its
-  // 16-byte chunk c sits at chunk (c ^ ((r >> 1) & 3))  (TMA 64B swizzle).
+  // byte offset of row (wrow + ty + 4*i) in an A tile and its swizzle term:
+  // row r lives at r*64 B, its 16-byte chunk c at chunk (c ^ ((r >> 1) & 3))  (TMA 64B swizzle)
+  const int a_row_base = (wrow + ty) * 64;
+  const int b_col_base = (wcol + tx * 4) * 4;
+
   int stage = 0;
   uint32_t phase = 0;
   bool ok = true;
   for (int kb = 0; kb < num_kb; kb++) {
-    ok = mbar_wait(&full[stage], phase, SITE_GEMM_MMA_FULL, wctx);
+    // refill the stage consumed one iteration ago, once every warp has released it
+    if (tid == 0 && kb >= 1 && kb - 1 + STAGES < num_kb) {
+      const int ps = (stage + STAGES - 1) % STAGES;
+      const uint32_t pphase = (ps == STAGES - 1) ? (phase ^ 1) : phase;  // phase of iteration kb-1
+      if (mbar_wait(&empty[ps], pphase, SITE_GEMM_PRODUCER_EMPTY, wctx)) issue(kb - 1 + STAGES, ps);
+    }
+    if (!mbar_wait(&full[stage], phase, SITE_GEMM_MMA_FULL, wctx)) {
+      ok = false;
+      break;
+    }
     const uint8_t* sA = smem + stage * STAGE_BYTES;
-    const float* sB = reinterpret_cast<const float*>(smem + stage * STAGE_BYTES + A_BYTES);
-    if (ok) {
+    const uint8_t* sB = smem + stage * STAGE_BYTES + A_BYTES;
 #pragma unroll
     for (int kc = 0; kc < BK / 4; kc++) {
       float4 a[8];
 #pragma unroll
       for (int i = 0; i < 8; i++) {
         const int r = wrow + ty + 4 * i;
-        a[i] = *reinterpret_cast<const float4*>(sA + r * 64 + ((kc ^ ((r >> 1) & 3)) << 4));
+        a[i] = *reinterpret_cast<const float4*>(sA + a_row_base + i * 256 + ((kc ^ ((r >> 1) & 3)) << 4));
       }
 #pragma unroll
       for (int kk = 0; kk < 4; kk++) {
-        const float* brow = sB + (kc * 4 + kk) * BN + wcol + tx * 4;
-        const float4 b0 = *reinterpret_cast<const float4*>(brow);
-        const float4 b1 = *reinterpret_cast<const float4*>(brow + 32);
-        const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+        const uint8_t* brow = sB + (kc * 4 + kk) * (BN * 4) + b_col_base;
+        const ulonglong2 b01 = *reinterpret_cast<const ulonglong2*>(brow);
+        const ulonglong2 b23 = *reinterpret_cast<const ulonglong2*>(brow + 128);
 #pragma unroll
         for (int i = 0; i < 8; i++) {
           const float av = kk == 0 ? a[i].x : kk == 1 ? a[i].y : kk == 2 ? a[i].z : a[i].w;
-#pragma unroll
-          for (int j = 0; j < 8; j++) acc[i][j] = fmaf(av, b[j], acc[i][j]);
+          const unsigned long long a2 = dup2(av);
+          ffma2(acc[i][0], a2, b01.x);
+          ffma2(acc[i][1], a2, b01.y);
+          ffma2(acc[i][2], a2, b23.x);
+          ffma2(acc[i][3], a2, b23.y);
         }
       }
     }
-    }
-    // every thread is done reading this stage; the vote keeps the exit uniform
-    // when a wait gave up
-    ok = __syncthreads_and(ok ? 1 : 0) != 0;
-    if (!ok) break;
-    if (tid == 0 && kb + STAGES < num_kb) issue(kb + STAGES, stage);
+    // this warp is done with the stage
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[stage]);
     if (++stage == STAGES) {
       stage = 0;
       phase ^= 1;
@@ -149,11 +183,12 @@ gemm_f32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           const int col = nb * BN + wcol + tx * 4 + 32 * j;
           if (col < p.N) {  // N is a multiple of 4
             const float4 old = *reinterpret_cast<const float4*>(crow + col);
+            const float2 lo = unpack2(acc[i][2 * j]), hi = unpack2(acc[i][2 * j + 1]);
             float4 o;
-            o.x = __fadd_rn(__fmul_rn(p.alpha, acc[i][4 * j + 0]), __fmul_rn(p.beta, old.x));
-            o.y = __fadd_rn(__fmul_rn(p.alpha, acc[i][4 * j + 1]), __fmul_rn(p.beta, old.y));
-            o.z = __fadd_rn(__fmul_rn(p.alpha, acc[i][4 * j + 2]), __fmul_rn(p.beta, old.z));
-            o.w = __fadd_rn(__fmul_rn(p.alpha, acc[i][4 * j + 3]), __fmul_rn(p.beta, old.w));
+            o.x = __fadd_rn(__fmul_rn(p.alpha, lo.x), __fmul_rn(p.beta, old.x));
+            o.y = __fadd_rn(__fmul_rn(p.alpha, lo.y), __fmul_rn(p.beta, old.y));
+            o.z = __fadd_rn(__fmul_rn(p.alpha, hi.x), __fmul_rn(p.beta, old.z));
+            o.w = __fadd_rn(__fmul_rn(p.alpha, hi.y), __fmul_rn(p.beta, old.w));
             *reinterpret_cast<float4*>(crow + col) = o;
           }
         }

@@ -189,7 +189,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int mb, nb;
       tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
       // the vote keeps the warp together: the TMEM loads below are warp-collective
-      if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full[acc], acc_phase, SITE_GEMM_EPI_TMEM_FULL, wctx))) break;
+      if (!PH_WARP_WAIT(&tmem_full[acc], acc_phase, SITE_GEMM_EPI_TMEM_FULL, wctx)) break;
       tc_fence_after_sync();
       const int row = mb * BM + q * 32 + lane;
       const bool row_ok = row < p.M;

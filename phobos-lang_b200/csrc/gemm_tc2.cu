@@ -1,0 +1,337 @@
+// Tensor-core GEMM for sm_100a on CTA pairs (tcgen05 cta_group::2):
+// C = alpha * A@B + beta * C with f16 A and B.
+//
+// Same operator as gemm_tc.cu (the reference's `gemm` in its two tensor-core
+// regimes, examples/gemm_fp16tc_fp32acc.ph and examples/gemm_fp16.ph), used for
+// problems large enough to fill the machine.  Two CTAs on neighbouring SMs own
+// one 256 x BN output tile: each CTA stages its own 128 rows of A and its own
+// half of the B columns, so a CTA moves (128 + BN/2) * 64 operand elements per
+// k-block into shared memory instead of (128 + BN) * 64 — the 1-CTA kernel is
+// bound by that L2 -> shared-memory traffic, not by the tensor pipe.  One thread
+// of the leader CTA issues the MMAs for the pair; completions are multicast to
+// the mbarriers of both CTAs.  No TMA multicast is used: every CTA loads its
+// own operand slices.
+//
+// Warp roles per CTA (192 threads): warp 0 TMA producer, warp 1 MMA issuer
+// (leader CTA only) and tensor-memory owner, warps 2..5 epilogue
+// (tcgen05.ld -> alpha*acc + beta*C_old -> global).  Two accumulator buffers of
+// 256 columns let the epilogue of tile i overlap the main loop of tile i+1.
+// BN is a run-time multiple of 16 (<= 256): 256 unless N is narrower.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace ph {
+namespace {
+
+constexpr int BM = 128;       // rows per CTA; 256 per pair
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;
+constexpr int STAGES = 6;
+constexpr int A_BYTES = BM * BK * 2;          // 16 KB
+constexpr int B_BYTES = BK * 128 * 2;         // 16 KB: up to 128 columns (two 64-column boxes) per CTA
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int TMEM_COLS = 512;
+constexpr int ACC_STRIDE = 256;               // tensor-memory columns per accumulator buffer
+
+struct Tc2Params {
+  int M, N, K;
+  int bn;                 // N extent of a pair tile
+  int tiles_m, tiles_n;   // pair tiles
+  int group_m;            // row-blocks per raster band
+  float alpha, beta;
+  void* C;
+  long long ldc;
+  uint32_t* status;
+};
+
+__device__ __forceinline__ void pair_tile_coords(int t, const Tc2Params& p, int& mb, int& nb) {
+  const int per_group = p.group_m * p.tiles_n;
+  const int g = t / per_group;
+  const int first_m = g * p.group_m;
+  const int gsize = min(p.group_m, p.tiles_m - first_m);
+  const int r = t - g * per_group;
+  mb = first_m + r % gsize;
+  nb = r / gsize;
+}
+
+template <bool ACC_F16, typename CT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Tc2Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full = bars;                       // used in the leader CTA
+  uint64_t* empty = bars + STAGES;             // one per CTA
+  uint64_t* tmem_full = bars + 2 * STAGES;     // one per CTA
+  uint64_t* tmem_empty = bars + 2 * STAGES + 2;  // used in the leader CTA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const WaitCtx wctx{abort_flag, p.status};
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int s = 0; s < 2; s++) {
+      mbar_init(&tmem_full[s], 1);
+      mbar_init(&tmem_empty[s], 8);  // four epilogue warps in each CTA of the pair
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers exist before anything signals them
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int half_n = p.bn >> 1;                 // B columns staged by each CTA
+  const int nbox = (half_n + 63) >> 6;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (both CTAs) --------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      const uint32_t stage_tx = 2u * static_cast<uint32_t>(A_BYTES + nbox * (BK * 128));
+      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+        int mb, nb;
+        pair_tile_coords(t, p, mb, nb);
+        const int row0 = mb * (2 * BM) + static_cast<int>(rank) * BM;
+        const int col0 = nb * p.bn + static_cast<int>(rank) * half_n;
+        for (int kb = 0; kb < num_kb; kb++) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, SITE_GEMM_PRODUCER_EMPTY, wctx)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full_leader = mapa_u32(smem_u32(&full[stage]), 0);
+          if (leader) mbar_arrive_expect_tx(&full[stage], stage_tx);  // bytes of both CTAs' loads
+          tma_load_2d_pair(sA + stage * A_BYTES, &tmA, full_leader, kb * BK, row0);
+          for (int j = 0; j < nbox; j++)
+            tma_load_2d_pair(sB + stage * B_BYTES + j * (BK * 128), &tmB, full_leader, col0 + j * 64, kb * BK);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (leader CTA) ----------------------
+    if (leader && lane == 0) {
+      const uint32_t idesc = umma_idesc_f16(2 * BM, p.bn, !ACC_F16, /*a_mn=*/false, /*b_mn=*/true);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, SITE_GEMM_MMA_TMEM_EMPTY, wctx)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * ACC_STRIDE;
+        for (int kb = 0; kb < num_kb; kb++) {
+          if (!mbar_wait(&full[stage], phase, SITE_GEMM_MMA_FULL, wctx)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(sA + stage * A_BYTES);
+          const uint32_t b_addr = smem_u32(sB + stage * B_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; k++) {
+            const uint64_t a_desc = umma_smem_desc(a_addr + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t b_desc = umma_smem_desc(b_addr + k * (UMMA_K * 128), BK * 128, 1024);
+            umma_f16_ss_pair(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair(&empty[stage], 0x3);  // both CTAs may refill this stage
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) umma_commit_pair(&tmem_full[acc], 0x3);
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (both CTAs) ---------------------------
+    const int q = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = pair; t < num_tiles; t += num_pairs) {
+      int mb, nb;
+      pair_tile_coords(t, p, mb, nb);
+      if (!PH_WARP_WAIT(&tmem_full[acc], acc_phase, SITE_GEMM_EPI_TMEM_FULL, wctx)) break;
+      tc_fence_after_sync();
+      const int row = mb * (2 * BM) + static_cast<int>(rank) * BM + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      CT* crow = reinterpret_cast<CT*>(p.C) + static_cast<long long>(row) * p.ldc;
+      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * ACC_STRIDE;
+      const int col_end = min(p.N, (nb + 1) * p.bn);
+      const int chunks = (p.bn + 31) >> 5;
+#pragma unroll 1
+      for (int c = 0; c < chunks; c++) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_addr + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = nb * p.bn + c * 32;
+        if (row_ok && col0 < col_end) {
+          if constexpr (sizeof(CT) == 4) {
+#pragma unroll
+            for (int v = 0; v < 8; v++) {
+              const int col = col0 + v * 4;
+              if (col < col_end) {
+                float4 old = *reinterpret_cast<const float4*>(crow + col);
+                float4 o;
+                o.x = __fadd_rn(__fmul_rn(p.alpha, __uint_as_float(r[v * 4 + 0])), __fmul_rn(p.beta, old.x));
+                o.y = __fadd_rn(__fmul_rn(p.alpha, __uint_as_float(r[v * 4 + 1])), __fmul_rn(p.beta, old.y));
+                o.z = __fadd_rn(__fmul_rn(p.alpha, __uint_as_float(r[v * 4 + 2])), __fmul_rn(p.beta, old.z));
+                o.w = __fadd_rn(__fmul_rn(p.alpha, __uint_as_float(r[v * 4 + 3])), __fmul_rn(p.beta, old.w));
+                *reinterpret_cast<float4*>(crow + col) = o;
+              }
+            }
+          } else {
+#pragma unroll
+            for (int v = 0; v < 4; v++) {
+              const int col = col0 + v * 8;
+              if (col < col_end) {
+                uint4 oldv = *reinterpret_cast<const uint4*>(crow + col);
+                const __half2* oh = reinterpret_cast<const __half2*>(&oldv);
+                uint4 outv;
+                __half2* outh = reinterpret_cast<__half2*>(&outv);
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                  float a0, a1;
+                  if constexpr (ACC_F16) {
+                    a0 = __half2float(__ushort_as_half(static_cast<unsigned short>(r[v * 8 + 2 * e] & 0xFFFF)));
+                    a1 = __half2float(__ushort_as_half(static_cast<unsigned short>(r[v * 8 + 2 * e + 1] & 0xFFFF)));
+                  } else {
+                    a0 = __uint_as_float(r[v * 8 + 2 * e]);
+                    a1 = __uint_as_float(r[v * 8 + 2 * e + 1]);
+                  }
+                  const float2 of = __half22float2(oh[e]);
+                  const float x = __fadd_rn(__fmul_rn(p.alpha, a0), __fmul_rn(p.beta, of.x));
+                  const float y = __fadd_rn(__fmul_rn(p.alpha, a1), __fmul_rn(p.beta, of.y));
+                  outh[e] = __floats2half2_rn(x, y);
+                }
+                *reinterpret_cast<uint4*>(crow + col) = outv;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&tmem_empty[acc]), 0));
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  }
+
+  // ------------------------------ teardown --------------------------------------
+  __syncwarp();
+  if (*abort_flag != 0) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA leaves while the peer may still read its shared memory or signal it
+  tc_fence_after_sync();
+  if (warp == 1) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+}
+
+template <bool ACC_F16, typename CT>
+cudaError_t launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const Tc2Params& p, int sm_count,
+                        cudaStream_t stream) {
+  auto kern = gemm_tc2_kernel<ACC_F16, CT>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  if (e != cudaSuccess) return e;
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int pairs = sm_count / 2;
+  const int grid = 2 * (tiles < pairs ? tiles : pairs);
+  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+// Pair-tile width: 256 columns unless N is narrower.  Narrower tiles that would
+// fill the last wave better were measured slower (4096^3: 1150 TFLOP/s at 256 vs
+// 1010 at 224 and 990 at 192): per k-block every CTA stages 16 KB of A whatever
+// the width, so a narrow tile moves more operand bytes per MMA cycle.
+int pick_pair_bn(int N) {
+  const int up = (N + 15) / 16 * 16;
+  return up < 256 ? up : 256;
+}
+
+int launch_gemm_tc_pair(const void* A, long long lda, const void* B, long long ldb, void* C, long long ldc, int M, int N,
+                        int K, float alpha, float beta, bool acc_f16, bool c_f16, int bn_override, int sm_count,
+                        uint32_t* status, cudaStream_t stream, const char** err) {
+  CUtensorMap tmA, tmB;
+  if (!make_tmap_2d(&tmA, A, TMAP_F16, M, K, lda, BM, BK, TMAP_SWIZZLE_128B) ||
+      !make_tmap_2d(&tmB, B, TMAP_F16, K, N, ldb, BK, 64, TMAP_SWIZZLE_128B)) {
+    *err = "cuTensorMapEncodeTiled failed (alignment or driver entry point)";
+    return -1;
+  }
+  Tc2Params p{};
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.bn = (bn_override >= 32 && bn_override <= 256 && bn_override % 16 == 0) ? bn_override
+                                                                           : pick_pair_bn(N);
+  p.tiles_m = (M + 2 * BM - 1) / (2 * BM);
+  p.tiles_n = (N + p.bn - 1) / p.bn;
+  // a raster band keeps about 32 MB of A rows hot in L2 while the B panels stream past
+  long long g = (32ll << 20) / (2ll * BM * static_cast<long long>(K) * 2);
+  p.group_m = static_cast<int>(g < 1 ? 1 : (g > 16 ? 16 : g));
+  p.alpha = alpha;
+  p.beta = beta;
+  p.C = C;
+  p.ldc = ldc;
+  p.status = status;
+  cudaError_t e;
+  if (!acc_f16 && !c_f16) {
+    e = launch_pair<false, float>(tmA, tmB, p, sm_count, stream);
+  } else if (acc_f16 && c_f16) {
+    e = launch_pair<true, __half>(tmA, tmB, p, sm_count, stream);
+  } else {
+    *err = "unsupported accumulator / output type combination";
+    return -2;
+  }
+  if (e != cudaSuccess) {
+    *err = cudaGetErrorString(e);
+    return -3;
+  }
+  return 0;
+}
+
+}  // namespace ph

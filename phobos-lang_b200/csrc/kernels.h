@@ -9,6 +9,10 @@ namespace ph {
 int launch_gemm_tc(const void* A, long long lda, const void* B, long long ldb, void* C, long long ldc, int M, int N,
                    int K, float alpha, float beta, bool acc_f16, bool c_f16, int bn_override, int sm_count,
                    uint32_t* status, cudaStream_t stream, const char** err);
+// gemm_tc2.cu — the same operator on CTA pairs (cta_group::2), for large problems.
+int launch_gemm_tc_pair(const void* A, long long lda, const void* B, long long ldb, void* C, long long ldc, int M, int N,
+                        int K, float alpha, float beta, bool acc_f16, bool c_f16, int bn_override, int sm_count,
+                        uint32_t* status, cudaStream_t stream, const char** err);
 
 // tmap.cu — TMA descriptors (cuTensorMapEncodeTiled through the runtime's driver entry point).
 enum TmapType { TMAP_F16 = 0, TMAP_F32 = 1 };
@@ -32,6 +36,8 @@ int launch_scale_f32(float* C, long long ldc, long long rows, long long cols, fl
 int launch_flash_f16(const void* Q, const void* K, const void* V, void* O, int out_f32, long long batch_heads,
                      int Nq, int Nk, int D, float scale, int sm_count, uint32_t* status, cudaStream_t stream,
                      const char** err);
+
+int set_flash_trace(unsigned long long* device_buf, unsigned long long words);
 
 // elementwise.cu — generator and conversions.
 int launch_fill_random(void* out, int dtype_is_f16, unsigned long long n, unsigned long long seed,
