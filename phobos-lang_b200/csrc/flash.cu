@@ -24,12 +24,14 @@
 //   warp 8     TMA producer: Q once, then K and V blocks of 128 keys through one
 //              ring of five slots (a block takes thousands of clocks to land while
 //              the MMAs saturate shared memory, so the ring runs two blocks ahead)
-//   warp 9     tcgen05.mma issuer: S_i = Q_i K^T into tensor memory, then
-//              O_i += P_i V with P_i read from tensor memory (it overwrites S_i).
-//              One issuer for both tiles: two issuer warps (one per tile) were
-//              measured 20% slower, the tensor pipe does not interleave two
-//              instruction streams well
-//   warps 10-11 idle (they complete the third warpgroup)
+//   warps 9,10 tcgen05.mma issuers, one per query tile: S_i = Q_i K^T into tensor
+//              memory, then O_i += P_i V with P_i read from tensor memory (it
+//              overwrites S_i).  They take strict turns, so the two tiles keep
+//              ping-ponging, but each issuer does the barrier waits of its next
+//              batch while the other one issues (a tcgen05.mma blocks its thread
+//              until the pipe accepts it; two free-running issuers fell into
+//              lockstep and were 20% slower)
+//   warp 11    idle (completes the third warpgroup)
 // Tensor memory columns: S0 | S1 | O0 | O1.
 //
 // Exponentials: a 128x128 score tile needs 16384 exp2; the MUFU unit delivers 16
@@ -156,7 +158,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* s_full = bars + 1 + 2 * RING;  // 2 (per query tile)
   uint64_t* p_full = s_full + 2;           // 2
   uint64_t* o_done = s_full + 4;           // 2
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 6);
+  uint64_t* turn = s_full + 6;             // 2 (issuer hand-off)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 8);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -170,12 +173,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mbar_init(q_full, 1);
     for (int s = 0; s < RING; s++) {
       mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
+      mbar_init(&kv_empty[s], 2);  // released by both issuers
     }
     for (int s = 0; s < 2; s++) {
       mbar_init(&s_full[s], 1);
-      mbar_init(&p_full[s], 128);
+      mbar_init(&p_full[s], 4);    // one arrival per softmax warp
       mbar_init(&o_done[s], 1);
+      mbar_init(&turn[s], 1);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -221,8 +225,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       }
     }
-  } else if (warp == 9) {
-    // ------------------------------ MMA issuer ---------------------------------
+  } else if (warp <= 10) {
+    // ------------------------------ MMA issuers (warp 9: tile 0, warp 10: tile 1) ---
     if (lane == 0) {
       // S = Q K^T : M=128 (queries), N=128 (keys), both operands K-major
       const uint32_t idesc_s = umma_idesc_f16(QT, KB, true, false, false) | (p.negate_q ? (1u << 13) : 0u);
@@ -264,50 +268,50 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           cpar ^= 1;
         }
       };
+      // Issuer warp 9 owns query tile 0, warp 10 tile 1.  They take turns: while
+      // one issues its 16 MMAs (each tcgen05.mma blocks its thread until the pipe
+      // accepts it, ~96 clocks), the other performs the barrier waits of its next
+      // batch, so the tensor pipe never idles behind a wait.  turn[t] is arrived by
+      // the other issuer when its batch is issued.
+      const int i = warp - 9;
       bool ok = mbar_wait(q_full, 0, SITE_FLASH_MMA, wctx) && mbar_wait(&kv_full[cur], cpar, SITE_FLASH_MMA, wctx);
       if (ok) {
         tc_fence_after_sync();
-        issue_s(0, cur);
-        umma_commit(&s_full[0]);
-        issue_s(1, cur);
-        umma_commit(&s_full[1]);
+        issue_s(i, cur);
+        umma_commit(&s_full[i]);
         umma_commit(&kv_empty[cur]);
         advance();
       }
-      unsigned long long* tb = (blockIdx.x == 0 && blockIdx.y == 0) ? p.trace : nullptr;
+      unsigned long long* tb = (blockIdx.x == 0 && blockIdx.y == 0 && i == 0) ? p.trace : nullptr;
       for (int j = 0; j < nkb && ok; j++) {
         stamp(tb, 2, j, 0);
         const int vs = cur;
         if (!mbar_wait(&kv_full[vs], cpar, SITE_FLASH_MMA, wctx)) break;
         advance();
         const int ks = cur;
-        const uint32_t kpar = cpar;
         const bool more = j + 1 < nkb;
-        if (more) advance();
-        for (int i = 0; i < 2; i++) {
-          stamp(tb, 2, j, 1 + 3 * i);
-          if (!mbar_wait(&p_full[i], j & 1, SITE_FLASH_MMA, wctx)) {
-            ok = false;
-            break;
-          }
-          stamp(tb, 2, j, 2 + 3 * i);
-          tc_fence_after_sync();
-          issue_pv(i, vs, j > 0);
-          if (i == 1) umma_commit(&kv_empty[vs]);
-          if (more) {
-            if (i == 0 && !mbar_wait(&kv_full[ks], kpar, SITE_FLASH_MMA, wctx)) {
-              ok = false;
-              break;
-            }
-            tc_fence_after_sync();
-            issue_s(i, ks);
-            umma_commit(&s_full[i]);
-            if (i == 1) umma_commit(&kv_empty[ks]);
-          } else {
-            umma_commit(&o_done[i]);
-          }
-          stamp(tb, 2, j, 3 + 3 * i);
+        if (more) {
+          if (!mbar_wait(&kv_full[ks], cpar, SITE_FLASH_MMA, wctx)) break;
+          advance();
         }
+        // my turn: tile 0 goes first in every round (its barrier passes once before any arrival)
+        if (!mbar_wait(&turn[i], i == 0 ? ((j & 1) ^ 1) : (j & 1), SITE_FLASH_MMA, wctx)) break;
+        stamp(tb, 2, j, 1);
+        // P_i is the late input: everything else has been waited for by now
+        if (!mbar_wait(&p_full[i], j & 1, SITE_FLASH_MMA, wctx)) break;
+        stamp(tb, 2, j, 2);
+        tc_fence_after_sync();
+        issue_pv(i, vs, j > 0);
+        umma_commit(&kv_empty[vs]);
+        if (more) {
+          issue_s(i, ks);
+          umma_commit(&s_full[i]);
+          umma_commit(&kv_empty[ks]);
+        } else {
+          umma_commit(&o_done[i]);
+        }
+        mbar_arrive(&turn[i ^ 1]);
+        stamp(tb, 2, j, 3);
       }
     }
   }
@@ -411,7 +415,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tmem_st_32x32b_x32(s_addr + 32, pk[1]);
       tmem_st_wait();
       tc_fence_before_sync();
-      mbar_arrive(&p_full[i]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[i]);
       stamp(tb, i, j, 5);
     }
 
