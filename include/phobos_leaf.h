@@ -119,6 +119,26 @@ PH_API int phobos_gemm(const PhTensor *A, const PhTensor *B, const PhTensor *C, 
                        int32_t kind, void *workspace, size_t workspace_bytes, void *stream);
 PH_API size_t phobos_gemm_workspace_bytes(int32_t kind, int32_t a_dtype, int64_t M, int64_t N, int64_t K);
 
+/* The same GEMM for callers that have no workspace to lend and may not allocate
+ * one (a pod whose whole device budget already went to its tile arena, a
+ * serving loop barred from the CUDA allocator, a host that owns all
+ * allocation).  It has no counterpart in the reference.  A, B and C are
+ * f32-stored (kind PH_GEMM_FP16TC_FP32ACC: A and B are rounded RN-even to f16
+ * on the way in); the rounded copies go to a fixed scratch array inside the
+ * library's device data, PH_NOALLOC_SCRATCH_BYTES per GPU for as long as the
+ * library is loaded.  Limit: 2*(M*K + K*N) bytes (each operand padded to 256)
+ * must fit, else PH_ERR_WORKSPACE.  The call allocates nothing and enqueues on
+ * `stream` like phobos_gemm.  The first call on a device looks up the scratch
+ * address (cudaGetSymbolAddress, with that device current); make that first call
+ * before any stream capture begins.  All calls on a device share the one scratch
+ * array, which keeps the previous call's bytes (nothing needs to start at zero:
+ * each call overwrites what it reads): calls whose kernels may overlap on the
+ * GPU (different streams, no ordering) race on it and must be serialised by the
+ * caller.                                                                      */
+#define PH_NOALLOC_SCRATCH_BYTES (8 << 20)
+PH_API int phobos_gemm_fp16tc_noalloc(const PhTensor *A, const PhTensor *B, const PhTensor *C, float alpha,
+                                      float beta, void *stream);
+
 /* The init leaf of a partitioned matmul: C = beta * C, or C = 0 when there is
  * no previous value (phobos-cluster/src/clustergen.rs:1276-1360; entry name
  * `<kernel>_init`, clustergen.rs:1288).  The step leaf is phobos_gemm with

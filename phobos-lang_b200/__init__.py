@@ -98,6 +98,7 @@ def lib() -> ctypes.CDLL:
             "phobos_device_status": (c.c_int, [vp, c.POINTER(u32)]),
             "phobos_gemm": (c.c_int, [TP, TP, TP, f32, f32, i32, vp, sz, vp]),
             "phobos_gemm_workspace_bytes": (sz, [i32, i32, i64, i64, i64]),
+            "phobos_gemm_fp16tc_noalloc": (c.c_int, [TP, TP, TP, f32, f32, vp]),
             "phobos_matmul_init": (c.c_int, [TP, f32, i32, vp]),
             "phobos_flash_attention": (c.c_int, [TP, TP, TP, TP, f32, i64, vp, sz, vp]),
             "phobos_flash_workspace_bytes": (sz, [i32, i64, i64, i64, i64]),
@@ -229,6 +230,22 @@ def gemm(A, B, C, alpha: float, beta: float, kind: int, workspace=None, stream=N
     wp, wn = _ws(workspace)
     check(lib().phobos_gemm(ctypes.byref(a), ctypes.byref(b), ctypes.byref(c), alpha, beta, kind, wp, wn,
                             _stream_ptr(stream)))
+
+
+NOALLOC_SCRATCH_BYTES = 8 << 20
+
+
+def gemm_fp16tc_noalloc(A, B, C, alpha: float, beta: float, stream=None) -> None:
+    """gemm_fp16tc_fp32acc on f32-stored A, B, C without a caller workspace and without any allocation.
+
+    For callers that cannot lend scratch memory and may not allocate it (a pod whose device budget is
+    all in its tile arena, a loop barred from the CUDA allocator): the rounded f16 copies of A and B
+    go to a fixed NOALLOC_SCRATCH_BYTES array inside the library, so 2*(M*K + K*N) bytes must fit.
+    All calls on a device share that array: do not let two of them overlap on the GPU.
+    """
+    a, b, c = tensor_desc(A), tensor_desc(B), tensor_desc(C)
+    check(lib().phobos_gemm_fp16tc_noalloc(ctypes.byref(a), ctypes.byref(b), ctypes.byref(c), alpha, beta,
+                                           _stream_ptr(stream)))
 
 
 def gemm_workspace_bytes(kind: int, a_dtype: int, M: int, N: int, K: int) -> int:
