@@ -177,7 +177,7 @@ int phobos_device_info(int device, PhDeviceInfo* out) {
   out->sm_clock_khz = clock_khz;
   out->total_mem_bytes = static_cast<int64_t>(prop.totalGlobalMem);
   out->fp32_peak_flops = static_cast<double>(prop.multiProcessorCount) * 128.0 * 2.0 * clock_khz * 1e3;
-  snprintf(out->name, sizeof(out->name), "%s", prop.name);
+  snprintf(out->name, sizeof(out->name), "%.63s", prop.name);
   return PH_OK;
 }
 

@@ -99,6 +99,17 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
   return r;
 }
 
+constexpr int EXP_F16X2 = 9;  // value of the EMU template parameter that selects the f16x2 exponential
+__device__ __forceinline__ uint32_t ex2_f16x2(uint32_t x) {
+  uint32_t y;
+  asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t hadd2_bits(uint32_t a, uint32_t b) {
+  uint32_t y;
+  asm("add.rn.f16x2 %0, %1, %2;" : "=r"(y) : "r"(a), "r"(b));
+  return y;
+}
 __device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
   float2 d;
   asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
@@ -385,31 +396,61 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       stamp(tb, i, j, 3);
       const float2 c2 = make_float2(c, c), neg_m2 = make_float2(-m2, -m2);
-      float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
       uint32_t pk[2][32];
+      if constexpr (EMU == EXP_F16X2) {
+        // Two exponentials per MUFU operation, in f16: the argument pair is rounded to
+        // f16x2 and ex2.approx.f16x2 returns the pair of probabilities already in the
+        // f16x2 form the P operand needs.  The row sum adds these f16 values (so O and l
+        // see the same p) in eight short f16x2 chains that are widened to f32 at the end.
+        uint32_t hs[8];
 #pragma unroll
-      for (int cc = 0; cc < 4; cc++) {
+        for (int a8 = 0; a8 < 8; a8++) hs[a8] = 0u;
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          const float2 x = ffma2(make_float2(__uint_as_float(sr[cc][e]), __uint_as_float(sr[cc][e + 1])), c2, neg_m2);
-          float2 pr;
-          if (((e >> 1) & 7) < EMU) {
-            pr = exp2_poly2(x);
-          } else {
-            pr.x = ex2_approx(x.x);
-            pr.y = ex2_approx(x.y);
+        for (int cc = 0; cc < 4; cc++) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            const float2 x = ffma2(make_float2(__uint_as_float(sr[cc][e]), __uint_as_float(sr[cc][e + 1])), c2, neg_m2);
+            uint32_t ph = ex2_f16x2(pack_f16x2(x.x, x.y));
+            if (valid < KB) {  // keys past the end contribute nothing
+              if (cc * 32 + e >= valid) ph &= 0xFFFF0000u;
+              if (cc * 32 + e + 1 >= valid) ph &= 0x0000FFFFu;
+            }
+            hs[(e >> 1) & 7] = hadd2_bits(hs[(e >> 1) & 7], ph);
+            pk[cc >> 1][(cc & 1) * 16 + (e >> 1)] = ph;
           }
-          if (valid < KB) {  // keys past the end contribute nothing
-            if (cc * 32 + e >= valid) pr.x = 0.0f;
-            if (cc * 32 + e + 1 >= valid) pr.y = 0.0f;
-          }
-          if ((e & 2) == 0) la = fadd2(la, pr);
-          else lb = fadd2(lb, pr);
-          pk[cc >> 1][(cc & 1) * 16 + (e >> 1)] = pack_f16x2(pr.x, pr.y);
         }
+        float sum = 0.0f;
+#pragma unroll
+        for (int a8 = 0; a8 < 8; a8++) {
+          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hs[a8]));
+          sum += f.x + f.y;
+        }
+        l += sum;
+      } else {
+        float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int cc = 0; cc < 4; cc++) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            const float2 x = ffma2(make_float2(__uint_as_float(sr[cc][e]), __uint_as_float(sr[cc][e + 1])), c2, neg_m2);
+            float2 pr;
+            if (((e >> 1) & 7) < EMU) {
+              pr = exp2_poly2(x);
+            } else {
+              pr.x = ex2_approx(x.x);
+              pr.y = ex2_approx(x.y);
+            }
+            if (valid < KB) {  // keys past the end contribute nothing
+              if (cc * 32 + e >= valid) pr.x = 0.0f;
+              if (cc * 32 + e + 1 >= valid) pr.y = 0.0f;
+            }
+            if ((e & 2) == 0) la = fadd2(la, pr);
+            else lb = fadd2(lb, pr);
+            pk[cc >> 1][(cc & 1) * 16 + (e >> 1)] = pack_f16x2(pr.x, pr.y);
+          }
+        }
+        l += (la.x + la.y) + (lb.x + lb.y);
       }
-      const float l0 = la.x, l1 = la.y, l2 = lb.x, l3 = lb.y;
-      l += (l0 + l1) + (l2 + l3);
       stamp(tb, i, j, 4);
       tmem_st_32x32b_x32(s_addr, pk[0]);
       tmem_st_32x32b_x32(s_addr + 32, pk[1]);
@@ -535,7 +576,8 @@ int launch_flash_f16(const void* Q, const void* K, const void* V, void* O, int o
   if (const char* ev = getenv("PHOBOS_FLASH_EMU")) emu = atoi(ev);
   cudaError_t e;
   if (D == 128 && !out_f32) {
-    e = emu == 2 ? launch_d<128, false, 2>(tmQ, tmK, tmV, p, batch_heads, stream)
+    e = emu == 9 ? launch_d<128, false, EXP_F16X2>(tmQ, tmK, tmV, p, batch_heads, stream)
+        : emu == 2 ? launch_d<128, false, 2>(tmQ, tmK, tmV, p, batch_heads, stream)
         : emu == 4 ? launch_d<128, false, 4>(tmQ, tmK, tmV, p, batch_heads, stream)
         : emu == 3 ? launch_d<128, false, 3>(tmQ, tmK, tmV, p, batch_heads, stream)
                    : launch_d<128, false, 0>(tmQ, tmK, tmV, p, batch_heads, stream);
