@@ -69,5 +69,22 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB
 
 
+def build_probes() -> Path:
+    """Compiles the diagnostic pipe-rate probe (csrc/probes/pipe_probe.cu) into phobos-lang_b200/pipe_probe."""
+    out = HERE / "pipe_probe"
+    env = dict(os.environ)
+    env.pop("CC", None)
+    env.pop("CXX", None)
+    cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-o", str(out),
+           str(CSRC / "probes" / "pipe_probe.cu")]
+    r = subprocess.run(cmd, capture_output=True, text=True, env=env)
+    if r.returncode != 0:
+        raise RuntimeError(f"nvcc failed for pipe_probe.cu:\n{r.stdout}\n{r.stderr}")
+    return out
+
+
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    if "--probes" in sys.argv:
+        print(build_probes())
+    else:
+        print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

@@ -19,6 +19,8 @@
 // BN is a run-time multiple of 16 (<= 256): 256 unless N is narrower.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -33,7 +35,9 @@ constexpr int STAGES = 6;
 constexpr int A_BYTES = BM * BK * 2;          // 16 KB
 constexpr int B_BYTES = BK * 128 * 2;         // 16 KB: up to 128 columns (two 64-column boxes) per CTA
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int EPI_LD = 36;                    // floats per row of an epilogue transpose pad (32 + 4: conflict-free)
+constexpr int EPI_BYTES = 4 * 32 * EPI_LD * 4; // one 32 x 32 pad per epilogue warp
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + EPI_BYTES;
 constexpr int TMEM_COLS = 512;
 constexpr int ACC_STRIDE = 256;               // tensor-memory columns per accumulator buffer
 
@@ -46,7 +50,44 @@ struct Tc2Params {
   void* C;
   long long ldc;
   uint32_t* status;
+  // split-K of the last, partly filled round of tiles (f32 C only): the `split_tiles`
+  // last tiles are each cut into `split` K ranges so that every CTA pair has work
+  int split;            // 1 = off
+  int split_first;      // index of the first split tile
+  uint32_t* flags;      // hand-over words between the K ranges of a tile
+  uint32_t epoch;       // distinguishes this launch's hand-overs from older ones
 };
+
+// Work unit u of a launch -> (tile, K range).  Units [0, split_first) are whole
+// tiles; after them come `split` consecutive units per remaining tile.
+struct Unit {
+  int tile, part, kb0, kb1;
+};
+__device__ __forceinline__ Unit unit_of(int u, const Tc2Params& p, int num_kb) {
+  Unit w;
+  if (u < p.split_first) {
+    w.tile = u;
+    w.part = 0;
+    w.kb0 = 0;
+    w.kb1 = num_kb;
+  } else {
+    const int v = u - p.split_first;
+    w.tile = p.split_first + v / p.split;
+    w.part = v % p.split;
+    w.kb0 = static_cast<int>(static_cast<long long>(num_kb) * w.part / p.split);
+    w.kb1 = static_cast<int>(static_cast<long long>(num_kb) * (w.part + 1) / p.split);
+  }
+  return w;
+}
+constexpr int FLAG_BANKS = 8, FLAG_TILES = 64;  // flags[bank][tile][cta][warp]
+__device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 
 __device__ __forceinline__ void pair_tile_coords(int t, const Tc2Params& p, int& mb, int& nb) {
   const int per_group = p.group_m * p.tiles_n;
@@ -72,6 +113,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   uint64_t* tmem_empty = bars + 2 * STAGES + 2;  // used in the leader CTA
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  float* epi_pad = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + 256);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -105,6 +147,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
   const int num_tiles = p.tiles_m * p.tiles_n;
   const int num_kb = (p.K + BK - 1) / BK;
+  const int num_units = p.split_first + (num_tiles - p.split_first) * p.split;
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
   const int half_n = p.bn >> 1;                 // B columns staged by each CTA
@@ -117,12 +160,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       uint32_t phase = 0;
       bool ok = true;
       const uint32_t stage_tx = 2u * static_cast<uint32_t>(A_BYTES + nbox * (BK * 128));
-      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+      for (int u = pair; u < num_units && ok; u += num_pairs) {
+        const Unit w = unit_of(u, p, num_kb);
         int mb, nb;
-        pair_tile_coords(t, p, mb, nb);
+        pair_tile_coords(w.tile, p, mb, nb);
         const int row0 = mb * (2 * BM) + static_cast<int>(rank) * BM;
         const int col0 = nb * p.bn + static_cast<int>(rank) * half_n;
-        for (int kb = 0; kb < num_kb; kb++) {
+        for (int kb = w.kb0; kb < w.kb1; kb++) {
           if (!mbar_wait(&empty[stage], phase ^ 1, SITE_GEMM_PRODUCER_EMPTY, wctx)) {
             ok = false;
             break;
@@ -148,11 +192,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+      for (int u = pair; u < num_units && ok; u += num_pairs) {
+        const Unit w = unit_of(u, p, num_kb);
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, SITE_GEMM_MMA_TMEM_EMPTY, wctx)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * ACC_STRIDE;
-        for (int kb = 0; kb < num_kb; kb++) {
+        for (int kb = w.kb0; kb < w.kb1; kb++) {
           if (!mbar_wait(&full[stage], phase, SITE_GEMM_MMA_FULL, wctx)) {
             ok = false;
             break;
@@ -164,7 +209,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           for (int k = 0; k < BK / UMMA_K; k++) {
             const uint64_t a_desc = umma_smem_desc(a_addr + k * (UMMA_K * 2), 16, 1024);
             const uint64_t b_desc = umma_smem_desc(b_addr + k * (UMMA_K * 128), BK * 128, 1024);
-            umma_f16_ss_pair(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16_ss_pair(d_tmem, a_desc, b_desc, idesc, (kb != w.kb0 || k != 0) ? 1u : 0u);
           }
           umma_commit_pair(&empty[stage], 0x3);  // both CTAs may refill this stage
           if (++stage == STAGES) {
@@ -184,17 +229,87 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const int q = warp & 3;
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int t = pair; t < num_tiles; t += num_pairs) {
+    for (int u = pair; u < num_units; u += num_pairs) {
+      const Unit w = unit_of(u, p, num_kb);
       int mb, nb;
-      pair_tile_coords(t, p, mb, nb);
+      pair_tile_coords(w.tile, p, mb, nb);
       if (!PH_WARP_WAIT(&tmem_full[acc], acc_phase, SITE_GEMM_EPI_TMEM_FULL, wctx)) break;
       tc_fence_after_sync();
+      // K range `part` of a split tile adds onto what range part-1 left in C: wait
+      // for the hand-over word of this warp's 32 rows (same CTA rank, same warp)
+      float beta = p.beta;
+      uint32_t* flag = nullptr;
+      if (u >= p.split_first) {
+        flag = p.flags + ((((p.epoch % FLAG_BANKS) * FLAG_TILES + (w.tile - p.split_first)) * 2 + rank) * 4 + q);
+        if (w.part > 0) {
+          beta = 1.0f;
+          uint32_t okw = 1;
+          if (lane == 0) {
+            const uint32_t want = p.epoch * 8u + static_cast<uint32_t>(w.part);
+            const uint64_t t0 = globaltimer_ns();
+            while (ld_acquire_u32(flag) != want) {
+              if (globaltimer_ns() - t0 > PH_WAIT_NS) {
+                okw = 0;
+                *abort_flag = SITE_GEMM_EPI_TMEM_FULL;
+                atomicCAS(p.status, 0u, SITE_GEMM_EPI_TMEM_FULL | (blockIdx.x << 8));
+                break;
+              }
+            }
+          }
+          okw = __shfl_sync(0xffffffffu, okw, 0);
+          if (!okw) break;
+        }
+      }
       const int row = mb * (2 * BM) + static_cast<int>(rank) * BM + q * 32 + lane;
       const bool row_ok = row < p.M;
       CT* crow = reinterpret_cast<CT*>(p.C) + static_cast<long long>(row) * p.ldc;
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * ACC_STRIDE;
       const int col_end = min(p.N, (nb + 1) * p.bn);
       const int chunks = (p.bn + 31) >> 5;
+      if constexpr (sizeof(CT) == 4) {
+        // f32 C.  The accumulator arrives one row per lane; going to global memory that
+        // way makes every warp instruction touch 32 different rows (16 useful bytes per
+        // 32-byte sector, poor DRAM locality: measured 17 us per tile).  Each 32x32 chunk
+        // is therefore transposed through a per-warp shared-memory pad so that a warp
+        // instruction covers 4 rows x 128 contiguous bytes; the C_old values of the
+        // chunk are requested before the transpose so their latency overlaps it.
+        float* pad = epi_pad + q * (32 * EPI_LD);
+        const int sub_row = lane >> 3, sub_col = (lane & 7) * 4;
+        const long long row_base = static_cast<long long>(mb) * (2 * BM) + static_cast<int>(rank) * BM + q * 32;
+#pragma unroll 1
+        for (int c = 0; c < chunks; c++) {
+          const int col = nb * p.bn + c * 32 + sub_col;
+          const bool col_ok = col < col_end;
+          float4 old[8];
+#pragma unroll
+          for (int it = 0; it < 8; it++) {
+            const long long rr = row_base + it * 4 + sub_row;
+            old[it] = (col_ok && rr < p.M) ? *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.C) + rr * p.ldc + col)
+                                           : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_addr + c * 32, r);
+          tmem_ld_wait();
+          __syncwarp();  // the previous chunk's reads of the pad are done
+#pragma unroll
+          for (int v = 0; v < 8; v++)
+            *reinterpret_cast<uint4*>(pad + lane * EPI_LD + v * 4) = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+          __syncwarp();
+#pragma unroll
+          for (int it = 0; it < 8; it++) {
+            const long long rr = row_base + it * 4 + sub_row;
+            if (col_ok && rr < p.M) {
+              const float4 a4 = *reinterpret_cast<const float4*>(pad + (it * 4 + sub_row) * EPI_LD + sub_col);
+              float4 o;
+              o.x = __fadd_rn(__fmul_rn(p.alpha, a4.x), __fmul_rn(beta, old[it].x));
+              o.y = __fadd_rn(__fmul_rn(p.alpha, a4.y), __fmul_rn(beta, old[it].y));
+              o.z = __fadd_rn(__fmul_rn(p.alpha, a4.z), __fmul_rn(beta, old[it].z));
+              o.w = __fadd_rn(__fmul_rn(p.alpha, a4.w), __fmul_rn(beta, old[it].w));
+              *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.C) + rr * p.ldc + col) = o;
+            }
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < chunks; c++) {
         uint32_t r[32];
@@ -202,21 +317,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         tmem_ld_wait();
         const int col0 = nb * p.bn + c * 32;
         if (row_ok && col0 < col_end) {
-          if constexpr (sizeof(CT) == 4) {
-#pragma unroll
-            for (int v = 0; v < 8; v++) {
-              const int col = col0 + v * 4;
-              if (col < col_end) {
-                float4 old = *reinterpret_cast<const float4*>(crow + col);
-                float4 o;
-                o.x = __fadd_rn(__fmul_rn(p.alpha, __uint_as_float(r[v * 4 + 0])), __fmul_rn(p.beta, old.x));
-                o.y = __fadd_rn(__fmul_rn(p.alpha, __uint_as_float(r[v * 4 + 1])), __fmul_rn(p.beta, old.y));
-                o.z = __fadd_rn(__fmul_rn(p.alpha, __uint_as_float(r[v * 4 + 2])), __fmul_rn(p.beta, old.z));
-                o.w = __fadd_rn(__fmul_rn(p.alpha, __uint_as_float(r[v * 4 + 3])), __fmul_rn(p.beta, old.w));
-                *reinterpret_cast<float4*>(crow + col) = o;
-              }
-            }
-          } else {
+          {
 #pragma unroll
             for (int v = 0; v < 4; v++) {
               const int col = col0 + v * 8;
@@ -246,8 +347,15 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           }
         }
       }
+      }
       tc_fence_before_sync();
       __syncwarp();
+      if (flag != nullptr && w.part + 1 < p.split) {
+        // this warp's rows of C are written: hand them to the next K range
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) st_release_u32(flag, p.epoch * 8u + static_cast<uint32_t>(w.part) + 1u);
+      }
       if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&tmem_empty[acc]), 0));
       if (++acc == 2) {
         acc = 0;
@@ -269,6 +377,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   if (warp == 1) tmem_dealloc_pair(tmem_base, TMEM_COLS);
 }
 
+// Hand-over words of the split-K tail, [bank][tile][cta][warp]; a launch uses bank
+// epoch % FLAG_BANKS, so up to FLAG_BANKS launches may be in flight on one device.
+__device__ uint32_t g_split_flags[FLAG_BANKS * FLAG_TILES * 2 * 4];
+uint32_t* g_split_flags_addr[64] = {};
+uint32_t g_epoch = 0;
+
 template <bool ACC_F16, typename CT>
 cudaError_t launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const Tc2Params& p, int sm_count,
                         cudaStream_t stream) {
@@ -277,7 +391,8 @@ cudaError_t launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const Tc
   if (e != cudaSuccess) return e;
   const int tiles = p.tiles_m * p.tiles_n;
   const int pairs = sm_count / 2;
-  const int grid = 2 * (tiles < pairs ? tiles : pairs);
+  const int units = p.split_first + (tiles - p.split_first) * p.split;
+  const int grid = 2 * (units < pairs ? units : pairs);
   kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, p);
   return cudaGetLastError();
 }
@@ -318,6 +433,35 @@ int launch_gemm_tc_pair(const void* A, long long lda, const void* B, long long l
   p.C = C;
   p.ldc = ldc;
   p.status = status;
+  // split-K tail: when the last round would leave most CTA pairs idle, its tiles can be
+  // cut into 2 or 4 K ranges that are added into C one after the other (f32 C only).
+  // Off unless PHOBOS_GEMM_SPLITK=1: measured on 4096^3 it is no faster (1141 vs 1151
+  // TFLOP/s), the K ranges of a tile serialise their epilogues at the very end.
+  const int tiles = p.tiles_m * p.tiles_n, pairs = sm_count / 2;
+  p.split = 1;
+  p.split_first = tiles;
+  p.flags = nullptr;
+  p.epoch = 0;
+  const int rem = tiles % pairs;
+  const int num_kb = (K + BK - 1) / BK;
+  const char* splitk = getenv("PHOBOS_GEMM_SPLITK");
+  if (!c_f16 && tiles > pairs && rem > 0 && rem <= FLAG_TILES && 2 * rem <= pairs && splitk && splitk[0] == '1') {
+    int split = (4 * rem <= pairs) ? 4 : 2;
+    while (split > 1 && num_kb / split < 8) split >>= 1;
+    int dev = 0;
+    if (split > 1 && cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64) {
+      if (g_split_flags_addr[dev] == nullptr) {
+        void* fp = nullptr;
+        if (cudaGetSymbolAddress(&fp, g_split_flags) == cudaSuccess) g_split_flags_addr[dev] = static_cast<uint32_t*>(fp);
+      }
+      if (g_split_flags_addr[dev] != nullptr) {
+        p.split = split;
+        p.split_first = tiles - rem;
+        p.flags = g_split_flags_addr[dev];
+        p.epoch = __atomic_add_fetch(&g_epoch, 1u, __ATOMIC_RELAXED);
+      }
+    }
+  }
   cudaError_t e;
   if (!acc_f16 && !c_f16) {
     e = launch_pair<false, float>(tmA, tmB, p, sm_count, stream);

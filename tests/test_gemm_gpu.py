@@ -197,3 +197,18 @@ def test_rejects_bad_descriptors(ph, dev):
     with pytest.raises(ph.PhobosError) as e:
         ph.launch("saxpy", [A], [])
     assert e.value.code == ph.PH_ERR_UNSUPPORTED
+
+
+def test_gemm_fp16tc_split_k_tail(ph, oracle, dev, monkeypatch):
+    """The optional split-K tail (last round of tiles cut into K ranges that add into C in turn)."""
+    import torch
+    monkeypatch.setenv("PHOBOS_GEMM_SPLITK", "1")
+    M, N, K = 4864, 1024, 1024          # 76 pair tiles on 74 pairs: 2 tiles left over -> 4 K ranges each
+    a, b, c = _inputs(oracle, M, N, K)
+    a16, b16 = oracle.fp16_round(a), oracle.fp16_round(b)
+    rows = np.unique(np.concatenate([np.arange(0, M, 97, dtype=np.uint64), np.arange(M - 512, M, 5, dtype=np.uint64)]))
+    want = oracle.gemm_rows(a16, b16, c, 0.5, 1.5, rows=rows)
+    A, B, C = _to(dev, a16, True), _to(dev, b16, True), _to(dev, c)
+    ph.gemm(A, B, C, 0.5, 1.5, ph.GEMM_FP16TC_FP32ACC)
+    assert ph.device_status() == 0
+    assert oracle.rel_frobenius(C.cpu().numpy()[rows.astype(int)], want) <= TOL_F16TC
