@@ -13,7 +13,7 @@
 using namespace ph;
 
 // ---- tcgen05.mma: `nissue` warps each issue a stream of 128 x N x 16 MMAs into their own accumulator
-__global__ void __launch_bounds__(128, 1) umma_rate(int ts_mode, int N, int b_mn, int nissue, int iters, long long* out) {
+__global__ void __launch_bounds__(128, 1) umma_rate(int ts_mode, int N, int b_mn, int nissue, int nacc, int whole_warp, int iters, long long* out) {
   extern __shared__ uint8_t raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   __shared__ uint64_t bar[4];
@@ -36,7 +36,7 @@ __global__ void __launch_bounds__(128, 1) umma_rate(int ts_mode, int N, int b_mn
   const int w = threadIdx.x >> 5;
   if (threadIdx.x == 0) tstart = clock64();
   __syncthreads();
-  if ((threadIdx.x & 31) == 0 && w < nissue) {
+  if (whole_warp == 0 && (threadIdx.x & 31) == 0 && w < nissue) {
     const uint32_t idesc = umma_idesc_f16(128, N, true, false, b_mn != 0);
     const uint32_t a = smem_u32(smem + w * 49152), b = smem_u32(smem + w * 49152 + 16384);
     const uint64_t ad0 = umma_smem_desc(a, 16, 1024);
@@ -48,15 +48,48 @@ __global__ void __launch_bounds__(128, 1) umma_rate(int ts_mode, int N, int b_mn
     for (int it = 0; it < iters; it++) {
 #pragma unroll
       for (int kk = 0; kk < 4; kk++) {
-        if (ts_mode) umma_f16_ts(d, a_tmem + kk * 8, bd0 + kk * bstep, idesc, 1);
-        else umma_f16_ss(d, ad0 + kk * 2, bd0 + kk * bstep, idesc, 1);
+        // with nacc > 1 this one thread rotates over nacc independent accumulators
+        const uint32_t dk = d + static_cast<uint32_t>((kk & (nacc - 1)) * N);  // nacc is a power of two
+        if (ts_mode) umma_f16_ts(dk, a_tmem + kk * 8, bd0 + kk * bstep, idesc, 1);
+        else umma_f16_ss(dk, ad0 + kk * 2, bd0 + kk * bstep, idesc, 1);
       }
     }
+    out[4 + w] = clock64() - tstart;  // the issue loop alone, before the MMAs are known complete
     umma_commit(&bar[w]);
     unsigned spins = 0;
     while (!mbar_try_wait(&bar[w], 0) && ++spins < (1u << 26)) {
     }
     out[w] = clock64() - tstart;
+  }
+  if (whole_warp != 0 && w < nissue) {
+    // every lane runs the loop and the descriptor arithmetic (warp-uniform values);
+    // only the tcgen05.mma itself is predicated on one elected lane
+    const uint32_t idesc = umma_idesc_f16(128, N, true, false, b_mn != 0);
+    const uint32_t a = smem_u32(smem + w * 49152), b = smem_u32(smem + w * 49152 + 16384);
+    const uint64_t ad0 = umma_smem_desc(a, 16, 1024);
+    const uint64_t bd0 = b_mn ? umma_smem_desc(b, 8192, 1024) : umma_smem_desc(b, 16, 1024);
+    const uint64_t bstep = b_mn ? (2048 >> 4) : (32 >> 4);
+    const uint32_t d = tb + w * N;
+    const uint32_t a_tmem = tb + 256 + (w & 1) * 64;
+#pragma unroll 1
+    for (int it = 0; it < iters; it++) {
+#pragma unroll
+      for (int kk = 0; kk < 4; kk++) {
+        if (elect_one()) {
+          if (ts_mode) umma_f16_ts(d, a_tmem + kk * 8, bd0 + kk * bstep, idesc, 1);
+          else umma_f16_ss(d, ad0 + kk * 2, bd0 + kk * bstep, idesc, 1);
+        }
+      }
+    }
+    if (elect_one()) {
+      out[4 + w] = clock64() - tstart;
+      umma_commit(&bar[w]);
+      unsigned spins = 0;
+      while (!mbar_try_wait(&bar[w], 0) && ++spins < (1u << 26)) {
+      }
+      out[w] = clock64() - tstart;
+    }
+    __syncwarp();
   }
   __syncthreads();
   if (threadIdx.x < 32) tmem_dealloc(tb, 512);
@@ -118,7 +151,7 @@ int main() {
       if (ni * c[1] > 512 || (c[0] && ni * c[1] > 256)) continue;  // accumulators (and the TMEM A operand) must fit 512 columns
       const int iters = 256;
       cudaMemset(d, 0, 64);
-      umma_rate<<<148, 128, 200 * 1024>>>(c[0], c[1], c[2], ni, iters, d);
+      umma_rate<<<148, 128, 200 * 1024>>>(c[0], c[1], c[2], ni, 1, 0, iters, d);
       cudaError_t e = cudaDeviceSynchronize();
       long long h[4];
       cudaMemcpy(h, d, 32, cudaMemcpyDeviceToHost);
@@ -128,6 +161,33 @@ int main() {
              c[2] ? "N" : "K", c[1], ni, static_cast<double>(mx) / (iters * 4 * ni), c[1] / 2,
              e == cudaSuccess ? "" : "  CUDA ERROR");
     }
+  printf("one issuing thread rotating over several accumulators (A from smem unless noted)\n");
+  const int rot[][3] = {{0, 128, 1}, {0, 256, 1}, {0, 64, 2}, {0, 64, 4}, {0, 128, 2}, {0, 128, 4}, {0, 256, 2}, {1, 64, 2}, {1, 64, 4}, {1, 128, 2}};
+  for (auto& c : rot) {
+    const int iters = 256;
+    cudaMemset(d, 0, 64);
+    umma_rate<<<148, 128, 200 * 1024>>>(c[0], c[1], 1, 1, c[2], 0, iters, d);
+    cudaError_t e = cudaDeviceSynchronize();
+    long long h[8];
+    cudaMemcpy(h, d, 64, cudaMemcpyDeviceToHost);
+    printf("  A from %s, N=%3d, 1 issuer, %d accumulators: %6.1f clk/MMA complete, %6.1f clk/MMA to issue  (ideal %3d)%s\n",
+           c[0] ? "TMEM" : "smem", c[1], c[2], static_cast<double>(h[0]) / (iters * 4), static_cast<double>(h[4]) / (iters * 4),
+           c[1] / 2, e == cudaSuccess ? "" : "  CUDA ERROR");
+  }
+  printf("whole warp runs the issue loop, one elected lane issues each MMA\n");
+  const int ww[][3] = {{0, 64, 1}, {0, 128, 1}, {0, 128, 2}, {0, 256, 1}, {0, 256, 2}, {1, 64, 1}, {1, 128, 1}, {1, 128, 2}, {1, 256, 1}};
+  for (auto& c : ww) {
+    const int iters = 256;
+    cudaMemset(d, 0, 64);
+    umma_rate<<<148, 128, 200 * 1024>>>(c[0], c[1], 1, c[2], 1, 1, iters, d);
+    cudaError_t e = cudaDeviceSynchronize();
+    long long h[8];
+    cudaMemcpy(h, d, 64, cudaMemcpyDeviceToHost);
+    long long mx = h[0] > h[1] ? h[0] : h[1];
+    printf("  A from %s, N=%3d, %d issuer(s): %6.1f clk/MMA complete, %6.1f clk/MMA to issue  (ideal %3d)%s\n",
+           c[0] ? "TMEM" : "smem", c[1], c[2], static_cast<double>(mx) / (iters * 4 * c[2]),
+           static_cast<double>(h[4]) / (iters * 4), c[1] / 2, e == cudaSuccess ? "" : "  CUDA ERROR");
+  }
   float* f;
   cudaMalloc(&f, 4);
   printf("fp32 fma from registers, 256 threads x 2 CTAs per SM\n");
