@@ -38,11 +38,11 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu
 # captures summarised under profiles/; None where no capture exists yet.
 NCU_TRAFFIC_BYTES = {
-    "gemm_fp16tc_fp32acc": None,
-    "gemm_fp32": None,
-    "gemm_fp16": None,
-    "flash_fp16": None,
-    "matmul_cluster_fp32": None,
+    "gemm_fp16tc_fp32acc": 152_248_320 + 40_332_544,       # profiles/gemm_tc2_fp16tc_fp32acc_4096.md
+    "gemm_fp32": 423_293_184 + 55_824_896,                 # profiles/gemm_f32_4096_and_16384.md
+    "gemm_fp16": 1_189_407_000 + 124_635_648,              # profiles/gemm_tc2_fp16_8192.md
+    "flash_fp16": 402_703_360 + 110_934_528,               # profiles/flash_fwd_fp16_bh128_s4096_d128.md
+    "matmul_cluster_fp32": 56_757_379_328 + 1_097_407_232,  # 16384^3 on one GPU, same file as gemm_fp32
 }
 
 
