@@ -138,6 +138,7 @@ class Ctx:
     def __init__(self, ph, torch, dev, steps, warmup):
         self.ph, self.torch, self.dev, self.steps, self.warmup = ph, torch, dev, steps, warmup
         self.windows = []
+        self.cpu_seconds = 1.0   # length of the CPU-baseline sample of the next workload
 
     def time_steps(self, fn_step, steps=None, warmup=None, barrier=None):
         """Runs warm-up steps, then times `steps` steps: total by one event pair around
@@ -241,7 +242,7 @@ def bench_gemm(ctx: Ctx, name: str, M: int, N: int, K: int, alpha: float, beta: 
                       + hC.numel() * hC.element_size(),
                       "d2h_bytes_per_step": hOut.numel() * hOut.element_size()}
     if cpu_baseline:
-        out["cpu_baseline"] = cpu_gemm_baseline(name, M, N, K, alpha, beta)
+        out["cpu_baseline"] = cpu_gemm_baseline(name, M, N, K, alpha, beta, min_seconds=ctx.cpu_seconds)
     del sets
     torch.cuda.empty_cache()
     return out
@@ -285,14 +286,14 @@ def bench_flash(ctx: Ctx, BH: int, S: int, D: int, peaks, cpu_baseline=True, e2e
         out["e2e"] = {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
                       "h2d_bytes_per_step": 3 * nb, "d2h_bytes_per_step": nb}
     if cpu_baseline:
-        out["cpu_baseline"] = cpu_flash_baseline(BH, S, D)
+        out["cpu_baseline"] = cpu_flash_baseline(BH, S, D, min_seconds=ctx.cpu_seconds)
     return out
 
 
 # ---------------------------------------------------------------------------------------------
 # CPU baseline: the oracle (port of the reference's f64 verifier arithmetic), bounded sample
 # ---------------------------------------------------------------------------------------------
-def cpu_gemm_baseline(name, M, N, K, alpha, beta, budget_flops=4e11):
+def cpu_gemm_baseline(name, M, N, K, alpha, beta, budget_flops=4e11, min_seconds=1.0):
     import numpy as np
     import oracle
     rows_n = int(max(64, min(M, budget_flops / (2.0 * N * K))))
@@ -305,27 +306,38 @@ def cpu_gemm_baseline(name, M, N, K, alpha, beta, budget_flops=4e11):
     c = oracle.lcg_fill(3, rows_n * N, scale).reshape(rows_n, N)
     if half:
         a, b = oracle.fp16_round(a), oracle.fp16_round(b)
+    reps = 0
     t0 = time.time()
-    oracle.gemm_rows(a, b, c, alpha, beta, rows=rows)
-    dt = time.time() - t0
-    fl = 2.0 * rows_n * N * K + rows_n * N
+    while True:   # the same rows again until the sample is long enough to time
+        oracle.gemm_rows(a, b, c, alpha, beta, rows=rows)
+        reps += 1
+        dt = time.time() - t0
+        if dt >= min_seconds or reps >= 64:
+            break
+    fl = (2.0 * rows_n * N * K + rows_n * N) * reps
     return {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": oracle.threads(), "kind": "port",
-            "sample": f"{rows_n} of {M} output rows x all {N} columns, K={K} (f64 accumulate, OpenMP); {dt:.2f} s"}
+            "sample": f"{reps} x ({rows_n} of {M} output rows x all {N} columns, K={K}; f64 accumulate, OpenMP); {dt:.2f} s"}
 
 
-def cpu_flash_baseline(BH, S, D, rows_n=256):
+def cpu_flash_baseline(BH, S, D, rows_n=4096, min_seconds=1.0):
     import numpy as np
     import oracle
     q = oracle.fp16_round(oracle.lcg_fill_normal(4, S * D)).reshape(S, D)
     k = oracle.fp16_round(oracle.lcg_fill_normal(5, S * D)).reshape(S, D)
     v = oracle.fp16_round(oracle.lcg_fill_normal(6, S * D)).reshape(S, D)
+    rows_n = min(rows_n, S)
     rows = np.arange(0, S, S // rows_n, dtype=np.uint64)[:rows_n]
+    reps = 0
     t0 = time.time()
-    oracle.flash_rows(q, k, v, 1.0 / math.sqrt(D), rows=rows)
-    dt = time.time() - t0
-    fl = 4.0 * rows.size * S * D
+    while True:
+        oracle.flash_rows(q, k, v, 1.0 / math.sqrt(D), rows=rows)
+        reps += 1
+        dt = time.time() - t0
+        if dt >= min_seconds or reps >= 64:
+            break
+    fl = 4.0 * rows.size * S * D * reps
     return {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": oracle.threads(), "kind": "port",
-            "sample": f"{rows.size} of {BH * S} query rows of one head, all {S} keys (f64 online softmax, OpenMP); {dt:.2f} s"}
+            "sample": f"{reps} x ({rows.size} of {BH * S} query rows, one head, all {S} keys; f64 online softmax, OpenMP); {dt:.2f} s"}
 
 
 # ---------------------------------------------------------------------------------------------
@@ -430,7 +442,7 @@ def run_reference(args, world, rank):
     vals = []
     sample = ""
     for i in range(args.warmup + args.steps):
-        r = cpu_gemm_baseline(name, M, N, K, alpha, beta, budget_flops=1.5e11)
+        r = cpu_gemm_baseline(name, M, N, K, alpha, beta, budget_flops=1.5e11, min_seconds=5.0)
         if i >= args.warmup:
             vals.append(r["value"])
         sample = r["sample"]
@@ -520,7 +532,9 @@ def main():
                                                   cpu_baseline=False, e2e=False),
     }
     head_name = args.only or "gemm_fp16tc_fp32acc"
+    ctx.cpu_seconds = 10.0     # the headline's CPU baseline gets a sample of about ten seconds
     head = runners[head_name]()
+    ctx.cpu_seconds = 1.0
     if not args.no_suite and not args.only:
         for name, fn in runners.items():
             if name != head_name:

@@ -12,8 +12,9 @@
 // the mbarriers of both CTAs.  No TMA multicast is used: every CTA loads its
 // own operand slices.
 //
-// Warp roles per CTA (192 threads): warp 0 TMA producer, warp 1 MMA issuer
-// (leader CTA only) and tensor-memory owner, warps 2..5 epilogue
+// Warp roles per CTA (256 threads): warp 0 TMA producer, warp 1 MMA issuer
+// (leader CTA only) and tensor-memory owner, warps 2 and 3 the same two roles for
+// an optional second tile in flight (idle by default), warps 4..7 epilogue
 // (tcgen05.ld -> alpha*acc + beta*C_old -> global).  Two accumulator buffers of
 // 256 columns let the epilogue of tile i overlap the main loop of tile i+1.
 // BN is a run-time multiple of 16 (<= 256): 256 unless N is narrower.
@@ -30,7 +31,7 @@ namespace {
 constexpr int BM = 128;       // rows per CTA; 256 per pair
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 256;
 constexpr int STAGES = 6;
 constexpr int A_BYTES = BM * BK * 2;          // 16 KB
 constexpr int B_BYTES = BK * 128 * 2;         // 16 KB: up to 128 columns (two 64-column boxes) per CTA
@@ -56,6 +57,9 @@ struct Tc2Params {
   int split_first;      // index of the first split tile
   uint32_t* flags;      // hand-over words between the K ranges of a tile
   uint32_t epoch;       // distinguishes this launch's hand-overs from older ones
+  // 2: two tiles of a pair are in flight at once, each with its own producer, issuer,
+  // accumulator buffer and half of the stage ring (see the kernel comment); 1: one tile
+  int streams;
 };
 
 // Work unit u of a launch -> (tile, K range).  Units [0, split_first) are whole
@@ -153,78 +157,88 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   const int half_n = p.bn >> 1;                 // B columns staged by each CTA
   const int nbox = (half_n + 63) >> 6;
 
-  if (warp == 0) {
-    // ------------------------------ TMA producer (both CTAs) --------------------
-    if (lane == 0) {
+  // Stream s (0 or 1) works on the pair's units n = s, s + streams, ... (unit n of a
+  // pair is launch unit pair + n * num_pairs), accumulates into buffer n & 1 and owns
+  // stages [s * ring, (s + 1) * ring) of the ring.
+  const int ring = STAGES / p.streams;
+  if (warp == 0 || warp == 2) {
+    // ------------------------------ TMA producers (both CTAs) -------------------
+    const int sidx = warp >> 1;
+    if (lane == 0 && sidx < p.streams) {
+      const int s0 = sidx * ring;
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       const uint32_t stage_tx = 2u * static_cast<uint32_t>(A_BYTES + nbox * (BK * 128));
-      for (int u = pair; u < num_units && ok; u += num_pairs) {
+      for (int n = sidx; ok; n += p.streams) {
+        const int u = pair + n * num_pairs;
+        if (u >= num_units) break;
         const Unit w = unit_of(u, p, num_kb);
         int mb, nb;
         pair_tile_coords(w.tile, p, mb, nb);
         const int row0 = mb * (2 * BM) + static_cast<int>(rank) * BM;
         const int col0 = nb * p.bn + static_cast<int>(rank) * half_n;
         for (int kb = w.kb0; kb < w.kb1; kb++) {
-          if (!mbar_wait(&empty[stage], phase ^ 1, SITE_GEMM_PRODUCER_EMPTY, wctx)) {
+          const int st = s0 + stage;
+          if (!mbar_wait(&empty[st], phase ^ 1, SITE_GEMM_PRODUCER_EMPTY, wctx)) {
             ok = false;
             break;
           }
-          const uint32_t full_leader = mapa_u32(smem_u32(&full[stage]), 0);
-          if (leader) mbar_arrive_expect_tx(&full[stage], stage_tx);  // bytes of both CTAs' loads
-          tma_load_2d_pair(sA + stage * A_BYTES, &tmA, full_leader, kb * BK, row0);
+          const uint32_t full_leader = mapa_u32(smem_u32(&full[st]), 0);
+          if (leader) mbar_arrive_expect_tx(&full[st], stage_tx);  // bytes of both CTAs' loads
+          tma_load_2d_pair(sA + st * A_BYTES, &tmA, full_leader, kb * BK, row0);
           for (int j = 0; j < nbox; j++)
-            tma_load_2d_pair(sB + stage * B_BYTES + j * (BK * 128), &tmB, full_leader, col0 + j * 64, kb * BK);
-          if (++stage == STAGES) {
+            tma_load_2d_pair(sB + st * B_BYTES + j * (BK * 128), &tmB, full_leader, col0 + j * 64, kb * BK);
+          if (++stage == ring) {
             stage = 0;
             phase ^= 1;
           }
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------ MMA issuer (leader CTA) ----------------------
-    if (leader && lane == 0) {
+  } else if (warp == 1 || warp == 3) {
+    // ------------------------------ MMA issuers (leader CTA) ---------------------
+    const int sidx = warp >> 1;
+    if (leader && lane == 0 && sidx < p.streams) {
       const uint32_t idesc = umma_idesc_f16(2 * BM, p.bn, !ACC_F16, /*a_mn=*/false, /*b_mn=*/true);
+      const int s0 = sidx * ring;
       int stage = 0;
       uint32_t phase = 0;
-      int acc = 0;
-      uint32_t acc_phase = 0;
       bool ok = true;
-      for (int u = pair; u < num_units && ok; u += num_pairs) {
+      for (int n = sidx; ok; n += p.streams) {
+        const int u = pair + n * num_pairs;
+        if (u >= num_units) break;
         const Unit w = unit_of(u, p, num_kb);
+        const int acc = n & 1;
+        const uint32_t acc_phase = (n >> 1) & 1;
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, SITE_GEMM_MMA_TMEM_EMPTY, wctx)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * ACC_STRIDE;
         for (int kb = w.kb0; kb < w.kb1; kb++) {
-          if (!mbar_wait(&full[stage], phase, SITE_GEMM_MMA_FULL, wctx)) {
+          const int st = s0 + stage;
+          if (!mbar_wait(&full[st], phase, SITE_GEMM_MMA_FULL, wctx)) {
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          const uint32_t a_addr = smem_u32(sA + stage * A_BYTES);
-          const uint32_t b_addr = smem_u32(sB + stage * B_BYTES);
+          const uint32_t a_addr = smem_u32(sA + st * A_BYTES);
+          const uint32_t b_addr = smem_u32(sB + st * B_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; k++) {
             const uint64_t a_desc = umma_smem_desc(a_addr + k * (UMMA_K * 2), 16, 1024);
             const uint64_t b_desc = umma_smem_desc(b_addr + k * (UMMA_K * 128), BK * 128, 1024);
             umma_f16_ss_pair(d_tmem, a_desc, b_desc, idesc, (kb != w.kb0 || k != 0) ? 1u : 0u);
           }
-          umma_commit_pair(&empty[stage], 0x3);  // both CTAs may refill this stage
-          if (++stage == STAGES) {
+          umma_commit_pair(&empty[st], 0x3);  // both CTAs may refill this stage
+          if (++stage == ring) {
             stage = 0;
             phase ^= 1;
           }
         }
         if (ok) umma_commit_pair(&tmem_full[acc], 0x3);
-        if (++acc == 2) {
-          acc = 0;
-          acc_phase ^= 1;
-        }
       }
     }
-  } else {
+  } else if (warp >= 4) {
     // ------------------------------ epilogue (both CTAs) ---------------------------
     const int q = warp & 3;
     int acc = 0;
@@ -462,6 +476,14 @@ int launch_gemm_tc_pair(const void* A, long long lda, const void* B, long long l
       }
     }
   }
+  // PHOBOS_GEMM_STREAMS=2 keeps two tiles of a pair in flight, each with its own producer,
+  // issuer thread and accumulator (two issuing threads overlap their MMAs in an idle-SM
+  // test: 151 against 171 clocks per 256-wide MMA).  Off by default: measured on the real
+  // kernel it gains nothing at 8192^3 (1548 TFLOP/s either way) and loses at 4096^3
+  // (1058 against 1150: with 3.46 tiles per pair the second stream only lengthens the tail).
+  p.streams = 1;
+  if (const char* sv = getenv("PHOBOS_GEMM_STREAMS")) p.streams = (sv[0] == '2') ? 2 : 1;
+  if (p.split > 1) p.streams = 1;  // the K ranges of a split tile must run one after the other
   cudaError_t e;
   if (!acc_f16 && !c_f16) {
     e = launch_pair<false, float>(tmA, tmB, p, sm_count, stream);

@@ -212,3 +212,17 @@ def test_gemm_fp16tc_split_k_tail(ph, oracle, dev, monkeypatch):
     ph.gemm(A, B, C, 0.5, 1.5, ph.GEMM_FP16TC_FP32ACC)
     assert ph.device_status() == 0
     assert oracle.rel_frobenius(C.cpu().numpy()[rows.astype(int)], want) <= TOL_F16TC
+
+
+def test_gemm_fp16tc_two_tiles_in_flight(ph, oracle, dev, monkeypatch):
+    """The optional second tile stream of the pair kernel (own producer, issuer and accumulator)."""
+    monkeypatch.setenv("PHOBOS_GEMM_STREAMS", "2")
+    M, N, K = 4864, 1280, 768           # 95 pair tiles on 74 pairs: pairs with one and with two tiles, ragged K ring
+    a, b, c = _inputs(oracle, M, N, K)
+    a16, b16 = oracle.fp16_round(a), oracle.fp16_round(b)
+    rows = np.unique(np.concatenate([np.arange(0, M, 61, dtype=np.uint64), np.arange(M - 256, M, 3, dtype=np.uint64)]))
+    want = oracle.gemm_rows(a16, b16, c, 0.5, 1.5, rows=rows)
+    A, B, C = _to(dev, a16, True), _to(dev, b16, True), _to(dev, c)
+    ph.gemm(A, B, C, 0.5, 1.5, ph.GEMM_FP16TC_FP32ACC)
+    assert ph.device_status() == 0
+    assert oracle.rel_frobenius(C.cpu().numpy()[rows.astype(int)], want) <= TOL_F16TC
