@@ -176,7 +176,14 @@ PH_API int phobos_flash_trace(uint64_t *device_buf, uint64_t n_words);
  * signature order; scalars carry their parameter position.  `grid` and `cta`
  * describe the reference's own device tiling and are validated for presence
  * only.  The GEMM regime follows from the element types unless `kind_hint`
- * (a PhGemmKind, or -1) says otherwise.                                       */
+ * (a PhGemmKind, or -1) says otherwise.  In a cluster plan "gemm" / "matmul" is
+ * the accumulate STEP leaf, C = alpha*(A@B) + C, which carries the kernel's
+ * scalar list but no longer uses beta (rewrite_step_store, phobos-cluster/src/
+ * clustergen.rs:1363-1399): pass `(kind or PH_KIND_AUTO) | PH_LAUNCH_STEP_LEAF`
+ * for it.  The executor does so by itself for a kernel whose `<name>_init` leaf is
+ * registered too.                                                              */
+#define PH_KIND_AUTO 0xFF
+#define PH_LAUNCH_STEP_LEAF 0x100
 PH_API int phobos_launch(const char *entry, const PhTensor *tensors, int32_t n_tensors, const PhScalar *scalars,
                          int32_t n_scalars, const uint32_t grid[3], const uint32_t cta[3], int32_t kind_hint,
                          void *workspace, size_t workspace_bytes, void *stream);
@@ -222,6 +229,7 @@ PH_API PhJob *phobos_job_parse(const char *path);               /* NULL on error
 PH_API PhJob *phobos_job_parse_text(const char *text, const char *origin, const char *source_text);
 PH_API void phobos_job_free(PhJob *job);
 PH_API const char *phobos_job_kernel_name(const PhJob *job);
+PH_API const char *phobos_job_source(const PhJob *job);   /* text of the `source =` file */
 PH_API int32_t phobos_job_n_dims(const PhJob *job);
 PH_API const char *phobos_job_dim_name(const PhJob *job, int32_t i);
 PH_API int64_t phobos_job_dim_value(const PhJob *job, int32_t i);
@@ -309,6 +317,87 @@ PH_API uint64_t phobos_executor_arena_used(const PhExecutor *ex);
 PH_API uint64_t phobos_executor_served_bytes(const PhExecutor *ex);  /* phobos-pod/src/server.rs:22 */
 /* Device address and residency of a tile (TileStore::addr/is_resident, tile_store.rs:134-140). */
 PH_API int phobos_executor_tile_addr(const PhExecutor *ex, uint64_t tile, void **addr_out, int32_t *resident_out);
+
+/* ---- `.ph` declarations and the cluster view of a kernel ------------------------------ *
+ * phobos_program_parse reads the attributes, name and parameter list of kernel
+ * `kernel_index` of a source text (grammar SPEC.md:5-58; phobos-lang/src/ast.rs:44-92)
+ * and, when the kernel carries `@cluster`, derives what phobos-cluster/src/
+ * clustergen.rs derives from it: supertile symbols per tensor axis, grid axes, access
+ * modes, the accumulate-step and init leaves (or the single leaf), scalar positions.
+ * No code is generated; the body is only scanned for slices and the final store.      */
+typedef struct PhProgram PhProgram;
+PH_API PhProgram *phobos_program_parse(const char *source_text, int32_t kernel_index);  /* NULL on error */
+PH_API void phobos_program_free(PhProgram *p);
+PH_API const char *phobos_program_kernel_name(const PhProgram *p);
+PH_API int32_t phobos_program_n_params(const PhProgram *p);
+PH_API const char *phobos_program_param_name(const PhProgram *p, int32_t i);
+PH_API int32_t phobos_program_param_is_tensor(const PhProgram *p, int32_t i);
+PH_API int32_t phobos_program_param_dtype(const PhProgram *p, int32_t i);
+PH_API int32_t phobos_program_param_rank(const PhProgram *p, int32_t i);
+PH_API const char *phobos_program_param_dim(const PhProgram *p, int32_t i, int32_t axis, int64_t *literal);
+PH_API int32_t phobos_program_n_attrs(const PhProgram *p);
+PH_API const char *phobos_program_attr_name(const PhProgram *p, int32_t i);
+PH_API int32_t phobos_program_has_attr(const PhProgram *p, const char *attr);
+/* expanded choices of `NAME in [..]` (two values = doubling steps, ast.rs:58-72) */
+PH_API int32_t phobos_program_search_choices(const PhProgram *p, const char *attr, const char *dim, int64_t *out,
+                                             int32_t cap);
+PH_API int32_t phobos_program_is_clustered(const PhProgram *p);   /* 0: see phobos_last_error */
+PH_API const char *phobos_program_describe(const PhProgram *p);   /* canonical text of the cluster program */
+PH_API int32_t phobos_program_n_leaves(const PhProgram *p);
+PH_API const char *phobos_program_leaf_entry(const PhProgram *p, int32_t i);   /* "<name>", "<name>_init" */
+PH_API int32_t phobos_program_n_tensors(const PhProgram *p);
+PH_API int32_t phobos_program_tensor_mode(const PhProgram *p, int32_t i);
+/* job-file bindings against the kernel signature (names, element types, ranks, dims, scalars) */
+PH_API int phobos_job_check(const PhJob *job, const PhProgram *p);
+
+/* ---- supertile planner ------------------------------------------------------------------ *
+ * plan / plan_with / plan_budgeted_with and recover_plan of phobos-sched/src/lib.rs:
+ * 99-234: owner-computes placement of every output supertile (linear index modulo the
+ * live nodes), tiles allocated at first use and stored / freed at last use, inputs from
+ * storage (policy 0, DirectLoad) or from the lowest-numbered consumer (policy 1,
+ * HomeLoadPeerFetch), segments cut by a memory budget.  The instructions are PhInstr
+ * records the executor takes as they are.                                              */
+typedef struct PhPlanRequest PhPlanRequest;
+typedef struct PhPlan PhPlan;
+PH_API PhPlanRequest *phobos_plan_request_new(uint32_t nodes, uint64_t budget_bytes, int32_t policy);
+PH_API void phobos_plan_request_free(PhPlanRequest *r);
+PH_API void phobos_plan_request_dim(PhPlanRequest *r, const char *name, int64_t value);
+PH_API void phobos_plan_request_super(PhPlanRequest *r, const char *name, int64_t value);
+PH_API void phobos_plan_request_scalar(PhPlanRequest *r, const char *name, int32_t dtype, uint64_t bits);
+PH_API void phobos_plan_request_default_supers(PhPlanRequest *r, const PhProgram *p);   /* first @cluster choice */
+/* turns the request into a recovery: `nodes` is the cluster width, `dead` every failed node,
+ * durable (tensor, linear index) pairs are not recomputed (lib.rs:172-234) */
+PH_API void phobos_plan_request_recover(PhPlanRequest *r, const uint32_t *dead, int32_t n_dead,
+                                        const uint32_t *durable_tensor, const uint64_t *durable_lin, int32_t n_durable,
+                                        uint16_t version, uint64_t iid_base);
+PH_API PhPlan *phobos_plan_make(const PhProgram *p, const PhPlanRequest *r);   /* NULL on error */
+PH_API void phobos_plan_free(PhPlan *pl);
+PH_API int phobos_plan_validate(const PhPlan *pl);                             /* lib.rs:950-974 */
+PH_API uint32_t phobos_plan_n_nodes(const PhPlan *pl);
+PH_API int32_t phobos_plan_n_segments(const PhPlan *pl, uint32_t node);
+PH_API uint64_t phobos_plan_segment_id(const PhPlan *pl, uint32_t node, int32_t seg);
+PH_API int32_t phobos_plan_segment_n_instrs(const PhPlan *pl, uint32_t node, int32_t seg);
+PH_API const PhInstr *phobos_plan_segment_instrs(const PhPlan *pl, uint32_t node, int32_t seg);
+PH_API void phobos_plan_segment_mem(const PhPlan *pl, uint32_t node, int32_t seg, uint64_t *peak, uint64_t *incremental);
+PH_API uint64_t phobos_plan_fetch_bytes(const PhPlan *pl);
+PH_API uint64_t phobos_plan_peak_resident(const PhPlan *pl);
+PH_API uint64_t phobos_plan_max_iid(const PhPlan *pl);
+PH_API int32_t phobos_plan_n_stores(const PhPlan *pl);
+PH_API void phobos_plan_store(const PhPlan *pl, int32_t i, uint64_t *iid, uint32_t *node, uint32_t *tensor, uint64_t *lin);
+PH_API int32_t phobos_plan_super_shape(const PhPlan *pl, uint32_t tensor, uint64_t *shape, uint64_t *grid, int32_t cap);
+PH_API int32_t phobos_plan_owner(const PhPlan *pl, uint32_t tensor, uint64_t lin);   /* -1: not in this plan */
+
+/* Ranks every combination of the @cluster choices by the makespan of its plan: busiest
+ * node's flops / leaf rate against busiest node's fetched bytes / link rate; configs that
+ * leave a node idle or exceed `vram_bytes` are dropped (phobos-sched/src/autotune.rs:40-192). */
+typedef struct PhTuneResult PhTuneResult;
+PH_API PhTuneResult *phobos_autotune(const PhProgram *p, const PhPlanRequest *dims_from, uint32_t nodes,
+                                     uint64_t vram_bytes, double link_bytes_per_sec, double leaf_flops_per_sec);
+PH_API void phobos_autotune_free(PhTuneResult *r);
+PH_API int32_t phobos_autotune_n(const PhTuneResult *r);
+PH_API int64_t phobos_autotune_super(const PhTuneResult *r, int32_t i, const char *name);
+PH_API void phobos_autotune_cost(const PhTuneResult *r, int32_t i, double *makespan, double *compute, double *comm,
+                                 uint64_t *peak, uint64_t *fetch_bytes);
 
 #ifdef __cplusplus
 }

@@ -119,6 +119,7 @@ def lib() -> ctypes.CDLL:
             "phobos_job_parse_text": (vp, [c.c_char_p, c.c_char_p, c.c_char_p]),
             "phobos_job_free": (None, [vp]),
             "phobos_job_kernel_name": (c.c_char_p, [vp]),
+            "phobos_job_source": (c.c_char_p, [vp]),
             "phobos_job_n_dims": (i32, [vp]),
             "phobos_job_dim_name": (c.c_char_p, [vp, i32]),
             "phobos_job_dim_value": (i64, [vp, i32]),
@@ -233,6 +234,8 @@ def gemm(A, B, C, alpha: float, beta: float, kind: int, workspace=None, stream=N
 
 
 NOALLOC_SCRATCH_BYTES = 8 << 20
+KIND_AUTO = 0xFF            # kind_hint: regime from the element types ...
+LAUNCH_STEP_LEAF = 0x100     # ... | this: gemm/matmul is the accumulate step of a cluster chain (beta unused)
 
 
 def gemm_fp16tc_noalloc(A, B, C, alpha: float, beta: float, stream=None) -> None:
@@ -343,6 +346,18 @@ def tile_fields(tid: int) -> tuple[int, int, int]:
     return int(L.phobos_tile_tensor(tid)), int(L.phobos_tile_version(tid)), int(L.phobos_tile_coord(tid))
 
 
+def tile_tensor(tid: int) -> int:
+    return tile_fields(tid)[0]
+
+
+def tile_version(tid: int) -> int:
+    return tile_fields(tid)[1]
+
+
+def tile_coord(tid: int) -> int:
+    return tile_fields(tid)[2]
+
+
 def size_class(nbytes: int) -> int:
     return int(lib().phobos_size_class(nbytes))
 
@@ -351,3 +366,5 @@ from .job import Job, parse_job, parse_job_text  # noqa: E402
 from .storage import load_region, storage_path, store_region  # noqa: E402
 from .executor import Executor, Instr  # noqa: E402
 from .partition import PartitionPlan, plan_partition  # noqa: E402
+from .planner import (DIRECT_LOAD, HOME_LOAD_PEER_FETCH, NO_BUDGET, Plan, Program, autotune, plan,  # noqa: E402
+                      run_plan)

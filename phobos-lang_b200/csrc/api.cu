@@ -344,8 +344,11 @@ int phobos_flash_trace(uint64_t* device_buf, uint64_t n_words) {
 }
 
 // ---- launch by entry name ---------------------------------------------------------------
+// kind_hint: -1, or a PhGemmKind / PH_KIND_AUTO in the low byte, optionally | PH_LAUNCH_STEP_LEAF
+static bool hint_is_step(int32_t kind_hint) { return kind_hint >= 0 && (kind_hint & PH_LAUNCH_STEP_LEAF) != 0; }
 static int gemm_kind_from_types(const PhTensor* t, int32_t kind_hint) {
-  if (kind_hint >= 0) return kind_hint;
+  const int base = kind_hint < 0 ? -1 : (kind_hint & 0xFF);
+  if (base >= 0 && base != PH_KIND_AUTO) return base;
   if (t[0].dtype == PH_F16 && t[2].dtype == PH_F16) return PH_GEMM_FP16;
   if (t[0].dtype == PH_F16 && t[2].dtype == PH_F32) return PH_GEMM_FP16TC_FP32ACC;
   return PH_GEMM_FP32;
@@ -394,8 +397,18 @@ int phobos_launch(const char* entry, const PhTensor* t, int32_t n_tensors, const
   if (!strcmp(entry, "gemm") || !strcmp(entry, "matmul")) {
     // gemm(A, B, C, alpha, beta): tensors at positions 0..2, scalars at 3 and 4
     if (n_tensors != 3) return fail(PH_ERR_INVALID, "%s takes 3 tensors, got %d", entry, n_tensors);
-    float alpha, beta;
-    if ((rc = scalar_f32(scalars, n_scalars, 3, &alpha)) || (rc = scalar_f32(scalars, n_scalars, 4, &beta))) return rc;
+    float alpha = 1.0f, beta = 1.0f;
+    if (hint_is_step(kind_hint)) {
+      // The accumulate step of a cluster chain (rewrite_step_store, phobos-cluster/src/
+      // clustergen.rs:1363-1399): C = alpha*(A@B) + C.  The COMPUTE still carries the
+      // kernel's own scalar list, but the leaf no longer uses beta (the init leaf applied
+      // it once); a kernel without an alpha parameter accumulates acc itself.
+      bool have_alpha = false;
+      for (int32_t i = 0; i < n_scalars; i++) have_alpha = have_alpha || scalars[i].pos == 3;
+      if (have_alpha && (rc = scalar_f32(scalars, n_scalars, 3, &alpha))) return rc;
+    } else {
+      if ((rc = scalar_f32(scalars, n_scalars, 3, &alpha)) || (rc = scalar_f32(scalars, n_scalars, 4, &beta))) return rc;
+    }
     return phobos_gemm(&t[0], &t[1], &t[2], alpha, beta, gemm_kind_from_types(t, kind_hint), workspace, workspace_bytes,
                        stream);
   }

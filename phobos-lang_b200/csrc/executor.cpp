@@ -366,8 +366,18 @@ void do_compute(PhExecutor* ex, uint64_t iid, const Node& n) {
       wrote = n.args[i].tile;
     }
   }
+  // a kernel that comes with an `<name>_init` leaf is the accumulate step of a chain
+  int32_t hint = k->second.kind_hint;
+  {
+    const std::string init_name = k->second.entry + "_init";
+    for (const auto& kv : ex->kernels)
+      if (kv.second.entry == init_name) {
+        hint = (hint < 0 ? PH_KIND_AUTO : (hint & 0xFF)) | PH_LAUNCH_STEP_LEAF;
+        break;
+      }
+  }
   const size_t need = phobos_launch_workspace_bytes(k->second.entry.c_str(), tensors.data(), (int32_t)tensors.size(),
-                                                    k->second.kind_hint);
+                                                    hint);
   if (need > ex->workspace_bytes) {
     // grown on demand, outside any steady state; kernels using the old buffer are drained first
     cudaDeviceSynchronize();
@@ -380,7 +390,7 @@ void do_compute(PhExecutor* ex, uint64_t iid, const Node& n) {
   // kernels that use the shared workspace are serialised on stream 0
   cudaStream_t s = need ? ex->streams[0] : pick_stream(ex);
   int rc = phobos_launch(k->second.entry.c_str(), tensors.data(), (int32_t)tensors.size(), n.scalars.data(),
-                         (int32_t)n.scalars.size(), n.in.grid, n.in.cta, k->second.kind_hint, ex->workspace,
+                         (int32_t)n.scalars.size(), n.in.grid, n.in.cta, hint, ex->workspace,
                          ex->workspace_bytes, s);
   if (rc) return fail_instr(ex, iid, rc, std::string("COMPUTE: ") + last_error());
   track(ex, s, iid, has_wrote, wrote, nullptr);

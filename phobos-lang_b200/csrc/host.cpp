@@ -383,6 +383,7 @@ PhJob* phobos_job_parse_text(const char* text, const char* origin, const char* s
 
 void phobos_job_free(PhJob* job) { delete job; }
 const char* phobos_job_kernel_name(const PhJob* j) { return j ? j->kernel.c_str() : ""; }
+const char* phobos_job_source(const PhJob* j) { return j ? j->source.c_str() : ""; }
 int32_t phobos_job_n_dims(const PhJob* j) { return j ? (int32_t)j->dims.size() : 0; }
 const char* phobos_job_dim_name(const PhJob* j, int32_t i) { return j->dims.at(i).name.c_str(); }
 int64_t phobos_job_dim_value(const PhJob* j, int32_t i) { return j->dims.at(i).value; }

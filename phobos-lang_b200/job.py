@@ -42,6 +42,14 @@ class Job:
     dims: dict = field(default_factory=dict)
     tensors: list = field(default_factory=list)
     scalars: list = field(default_factory=list)
+    source: str = ""                    # text of the `source =` file
+    _handle: object = field(default=None, repr=False, compare=False)
+
+    def __del__(self):
+        if self._handle:
+            from . import lib
+            lib().phobos_job_free(self._handle)
+            self._handle = None
 
 
 def _collect(handle) -> Job:
@@ -62,9 +70,12 @@ def _collect(handle) -> Job:
             job.scalars.append(JobScalar(name=L.phobos_job_scalar_name(handle, i).decode(),
                                          dtype=int(L.phobos_job_scalar_dtype(handle, i)),
                                          bits=int(L.phobos_job_scalar_bits(handle, i))))
+        job.source = L.phobos_job_source(handle).decode()
+        job._handle = handle
         return job
-    finally:
+    except Exception:
         L.phobos_job_free(handle)
+        raise
 
 
 def parse_job(path: str) -> Job:

@@ -30,7 +30,10 @@ def test_device_generator_matches_oracle(ph, oracle, dev):
 
 def test_matmul_job_through_the_executor(ph, oracle, dev, tmp_path):
     """ALLOC, LOAD, COMPUTE(init), COMPUTE(step) x2, STORE, FREE with dependencies, for a 2x1x2 split of
-    a 256x128x256 matmul read from and written to file:// tensors (cf. phobos-pod/examples/loopback.rs)."""
+    a 256x128x256 matmul read from and written to file:// tensors (cf. phobos-pod/examples/loopback.rs).
+    As in a reference plan the step COMPUTEs carry the kernel's whole scalar list (alpha AND the job's
+    beta = 1.5), but the step leaf is C = alpha*A@B + C: beta was applied once by the init leaf
+    (phobos-cluster/src/clustergen.rs:1363-1399)."""
     M, N, K = 256, 128, 256
     a = oracle.lcg_fill(1, M * K).reshape(M, K)
     b = oracle.lcg_fill(2, K * N).reshape(K, N)
@@ -67,7 +70,7 @@ def test_matmul_job_through_the_executor(ph, oracle, dev, tmp_path):
                 al = add(op=ph.OP_ALLOC, tile=at, shape=(MT, KT), data_type=ph.F32)
                 ld = add(op=ph.OP_LOAD, tile=at, tensor=0, region_offset=(mt * MT, kt * KT), region_shape=(MT, KT), deps=(al,))
                 prev = add(op=ph.OP_COMPUTE, kernel=0, args=((at, ph.READ), (b_loads[kt][0], ph.READ), (ct, ph.RMW)),
-                           scalars=(ph.scalar_f32(3, 0.125), ph.scalar_f32(4, 1.0)), grid=(4, 4, 1), deps=(ld, b_loads[kt][1], prev))
+                           scalars=(ph.scalar_f32(3, 0.125), ph.scalar_f32(4, 1.5)), grid=(4, 4, 1), deps=(ld, b_loads[kt][1], prev))
                 add(op=ph.OP_FREE, tile=at, deps=(prev,))
             st = add(op=ph.OP_STORE, tile=ct, tensor=2, region_offset=(mt * MT, 0), region_shape=(MT, N), deps=(prev,))
             last.append(add(op=ph.OP_FREE, tile=ct, deps=(st,)))

@@ -1,0 +1,134 @@
+"""Job file -> kernel declaration -> supertile plan -> executors, on a B200 (one or two nodes of one box)."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+GEMM_PH = """
+@cluster(SM in [256, 1024], SN in [256, 1024], SK in [256, 1024])
+@autotune(SM in [32, 256], SN in [32, 256], SK in [4, 32])
+kernel gemm(A: tensor<f32>[M, K], B: tensor<f32>[K, N], C: tensor<f32>[M, N], alpha: f32, beta: f32) {
+  let i = program_id(0)
+  let j = program_id(1)
+  var acc: tile<f32>[SM, SN] = 0.0
+  for k0 in range(0, K, SK) {
+    acc += dot(A[i * SM :+ SM, k0 :+ SK], B[k0 :+ SK, j * SN :+ SN])
+  }
+  let before = C[i * SM :+ SM, j * SN :+ SN]
+  C[i * SM :+ SM, j * SN :+ SN] = alpha * acc + beta * before
+}
+"""
+
+FLASH_PH = """
+@cluster(ROWS in [512, 2048])
+@tensorcore
+@launch(128)
+@autotune(D in [128], ROWS in [4, 128], COLS in [4, 128])
+kernel flash_attention(Q: tensor<f16>[Nq, D], K: tensor<f16>[Nk, D], V: tensor<f16>[Nk, D], O: tensor<f16>[Nq, D],
+                       scale: f32) {
+  let first = program_id(0) * ROWS
+  let q = Q[first :+ ROWS, :]
+  var acc: tile<f32>[ROWS, D] = 0.0
+  var top: tile<f32>[ROWS, 1] = -65504.0
+  var den: tile<f32>[ROWS, 1] = 0.0
+  for c0 in range(0, Nk, COLS) {
+    var s: tile<f32>[ROWS, COLS] = dot_t(q, K[c0 :+ COLS, :])
+    s = s * scale
+    var now: tile<f32>[ROWS, 1] = tmax(top, rowmax(s))
+    s = exp(s - now)
+    var fix: tile<f32>[ROWS, 1] = exp(top - now)
+    den = den * fix
+    den += rowsum(s)
+    acc = acc * fix
+    acc += dot(s, V[c0 :+ COLS, :])
+    top = now
+  }
+  acc = acc / den
+  O[first :+ ROWS, :] = acc
+}
+"""
+
+
+def _tensors(job):
+    return [(t.uri, t.dtype, t.shape, t.mode) for t in job.tensors]
+
+
+@pytest.mark.parametrize("nodes,policy", [(1, "direct"), (2, "direct"), (2, "fetch")])
+def test_gemm_job_planned_and_executed(ph, oracle, dev, tmp_path, nodes, policy):
+    """`C = alpha*A@B + beta*C` from a job file: beta once by the init leaf, then K/SK accumulate steps per
+    C supertile (which all carry the job's beta and must ignore it), outputs stored by their owners."""
+    import torch
+    M, N, K = 1024, 512, 768
+    a = oracle.lcg_fill(1, M * K).reshape(M, K)
+    b = oracle.lcg_fill(2, K * N).reshape(K, N)
+    c = oracle.lcg_fill(3, M * N).reshape(M, N)
+    for name, x in zip("abc", (a, b, c)):
+        ph.store_region(f"file://{tmp_path}/{name}.tensor", x.shape, (0, 0), x)
+    (tmp_path / "gemm.ph").write_text(GEMM_PH)
+    (tmp_path / "job.txt").write_text(f"""
+# C = 0.125 * A @ B + 1.5 * C
+source = {tmp_path}/gemm.ph
+dim M = {M}
+dim N = {N}
+dim K = {K}
+tensor A = read f32 {M}x{K} file://{tmp_path}/a.tensor
+tensor B = read f32 {K}x{N} file://{tmp_path}/b.tensor
+tensor C = rmw  f32 {M}x{N} file://{tmp_path}/c.tensor
+scalar alpha = f32 0.125
+scalar beta = f32 1.5
+""")
+    job = ph.parse_job(str(tmp_path / "job.txt"))
+    prog = ph.Program(job.source)
+    assert prog.name == job.kernel == "gemm"
+    prog.check_job(job)
+    scalars = {s.name: ph.PhScalar(0, s.dtype, s.bits) for s in job.scalars}
+    pl = ph.plan(prog, job.dims, nodes=nodes, scalars=scalars,
+                 policy=ph.HOME_LOAD_PEER_FETCH if policy == "fetch" else ph.DIRECT_LOAD)
+    pl.validate()
+    assert len(pl.stores) == (M // 256) * (N // 256)
+    if policy == "fetch":
+        assert pl.fetch_bytes > 0
+    ndev = torch.cuda.device_count()
+    exs = [ph.Executor(n if n < ndev else 0, n, 16 << 20) for n in range(nodes)]
+    try:
+        ph.run_plan(pl, prog, _tensors(job), exs)
+        for n, ex in enumerate(exs):
+            done = ex.completions()
+            assert sorted(d[0] for d in done) == sorted(i.iid for i in pl.node_instrs(n))
+            assert all(d[1] == 0 for d in done) and ex.arena_used == 0
+        if policy == "fetch":
+            assert sum(ex.served_bytes for ex in exs) == pl.fetch_bytes
+    finally:
+        for ex in exs:
+            ex.close()
+    got = ph.load_region(f"file://{tmp_path}/c.tensor", (M, N), (0, 0), (M, N))
+    assert oracle.rel_frobenius(got, oracle.gemm_rows(a, b, c, 0.125, 1.5)) <= 1e-5
+
+
+def test_flash_job_planned_and_executed(ph, oracle, dev, tmp_path):
+    """A kernel without a cluster loop is one leaf per query supertile; K and V are loaded whole."""
+    Nq, Nk, D = 1024, 640, 128
+    q, k, v = (oracle.fp16_round(oracle.lcg_fill_normal(s, n * D)).reshape(n, D) for s, n in ((4, Nq), (5, Nk), (6, Nk)))
+    for name, x in zip("qkv", (q, k, v)):
+        ph.store_region(f"file://{tmp_path}/{name}.tensor", x.shape, (0, 0), x.astype(np.float16))
+    ph.store_region(f"file://{tmp_path}/o.tensor", (Nq, D), (0, 0), np.zeros((Nq, D), np.float16))
+    job = ph.parse_job_text(f"""
+source = flash.ph
+tensor Q = read f16 {Nq}x{D} file://{tmp_path}/q.tensor
+tensor K = read f16 {Nk}x{D} file://{tmp_path}/k.tensor
+tensor V = read f16 {Nk}x{D} file://{tmp_path}/v.tensor
+tensor O = write f16 {Nq}x{D} file://{tmp_path}/o.tensor
+scalar scale = f32 0.08838834764831845
+""", "job.txt", FLASH_PH)
+    prog = ph.Program(job.source)
+    prog.check_job(job)
+    dims = {"Nq": Nq, "Nk": Nk, "D": D}
+    pl = ph.plan(prog, dims, scalars={"scale": ph.PhScalar(0, job.scalars[0].dtype, job.scalars[0].bits)})
+    pl.validate()
+    assert sum(1 for i in pl.node_instrs(0) if i.op == ph.OP_COMPUTE) == Nq // 512
+    with ph.Executor(0, 0, 16 << 20) as ex:
+        ph.run_plan(pl, prog, _tensors(job), [ex])
+        assert all(d[1] == 0 for d in ex.completions()) and ex.arena_used == 0
+    got = ph.load_region(f"file://{tmp_path}/o.tensor", (Nq, D), (0, 0), (Nq, D), dtype=ph.F16).astype(np.float32)
+    want = oracle.flash_rows(q, k, v, 0.08838834764831845)
+    assert oracle.rel_frobenius(got, want) <= 2e-3
