@@ -140,7 +140,7 @@ class Ctx:
         self.windows = []
         self.cpu_seconds = 1.0   # length of the CPU-baseline sample of the next workload
 
-    def time_steps(self, fn_step, steps=None, warmup=None, barrier=None):
+    def time_steps(self, fn_step, steps=None, warmup=None, barrier=None, finish=None):
         """Runs warm-up steps, then times `steps` steps: total by one event pair around
         the region (for `value`) and each launch by its own event pair (for the roofline)."""
         torch = self.torch
@@ -148,6 +148,8 @@ class Ctx:
         warmup = self.warmup if warmup is None else warmup
         for i in range(warmup):
             fn_step(i)
+        if finish:
+            finish()
         torch.cuda.synchronize()
         if barrier:
             barrier()
@@ -160,6 +162,8 @@ class Ctx:
             evs[i][0].record()
             fn_step(warmup + i)
             evs[i][1].record()
+        if finish:
+            finish()       # work on side streams: the closing event waits for it
         t1.record()
         torch.cuda.synchronize()
         if barrier:
@@ -229,14 +233,16 @@ def bench_gemm(ctx: Ctx, name: str, M: int, N: int, K: int, alpha: float, beta: 
         hA, hB, hC = pinned_like(torch, A), pinned_like(torch, B), pinned_like(torch, C)
         hOut = torch.empty(C.shape, dtype=C.dtype, device="cpu", pin_memory=True)
 
-        def e2e_step(i):
-            A.copy_(hA, non_blocking=True)
-            B.copy_(hB, non_blocking=True)
-            C.copy_(hC, non_blocking=True)
-            ph.gemm(A, B, C, alpha, beta, kind)
-            hOut.copy_(C, non_blocking=True)
+        # every step uploads A, B and C_old from pinned host memory and downloads C; the copies of
+        # neighbouring steps overlap the kernel (HostPipeline: three streams, two device buffer sets)
+        pipe = ph.HostPipeline(torch, dev, [(t.shape, t.dtype) for t in (A, B, C)],
+                               lambda a, b, c, stream: ph.gemm(a, b, c, alpha, beta, kind, stream=stream), result_index=2)
 
-        ms_e2e, _, _ = ctx.time_steps(e2e_step, steps=max(3, min(ctx.steps, 10)), warmup=3)
+        def e2e_step(i):
+            pipe.submit((hA, hB, hC), hOut)
+
+        ms_e2e, _, _ = ctx.time_steps(e2e_step, steps=max(6, min(ctx.steps, 20)), warmup=3, finish=pipe.join)
+        del pipe
         out["e2e"] = {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
                       "h2d_bytes_per_step": hA.numel() * hA.element_size() + hB.numel() * hB.element_size()
                       + hC.numel() * hC.element_size(),
@@ -274,14 +280,14 @@ def bench_flash(ctx: Ctx, BH: int, S: int, D: int, peaks, cpu_baseline=True, e2e
         hQ, hK, hV = (pinned_like(torch, t) for t in (Q, K, V))
         hO = torch.empty(O.shape, dtype=O.dtype, device="cpu", pin_memory=True)
 
-        def e2e_step(i):
-            Q.copy_(hQ, non_blocking=True)
-            K.copy_(hK, non_blocking=True)
-            V.copy_(hV, non_blocking=True)
-            ph.flash_attention(Q, K, V, O, scale)
-            hO.copy_(O, non_blocking=True)
+        pipe = ph.HostPipeline(torch, dev, [(t.shape, t.dtype) for t in (Q, K, V, O)],
+                               lambda q, k, v, o, stream: ph.flash_attention(q, k, v, o, scale, stream=stream), result_index=3)
 
-        ms_e2e, _, _ = ctx.time_steps(e2e_step, steps=max(3, min(ctx.steps, 10)), warmup=3)
+        def e2e_step(i):
+            pipe.submit((hQ, hK, hV, None), hO)
+
+        ms_e2e, _, _ = ctx.time_steps(e2e_step, steps=max(6, min(ctx.steps, 20)), warmup=3, finish=pipe.join)
+        del pipe
         nb = Q.numel() * 2
         out["e2e"] = {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
                       "h2d_bytes_per_step": 3 * nb, "d2h_bytes_per_step": nb}

@@ -366,5 +366,6 @@ from .job import Job, parse_job, parse_job_text  # noqa: E402
 from .storage import load_region, storage_path, store_region  # noqa: E402
 from .executor import Executor, Instr  # noqa: E402
 from .partition import PartitionPlan, plan_partition  # noqa: E402
+from .hostpipe import HostPipeline  # noqa: E402
 from .planner import (DIRECT_LOAD, HOME_LOAD_PEER_FETCH, NO_BUDGET, Plan, Program, autotune, plan,  # noqa: E402
                       run_plan)

@@ -226,3 +226,23 @@ def test_gemm_fp16tc_two_tiles_in_flight(ph, oracle, dev, monkeypatch):
     ph.gemm(A, B, C, 0.5, 1.5, ph.GEMM_FP16TC_FP32ACC)
     assert ph.device_status() == 0
     assert oracle.rel_frobenius(C.cpu().numpy()[rows.astype(int)], want) <= TOL_F16TC
+
+
+def test_host_pipeline_matches_direct_calls(ph, oracle, dev):
+    """Calls on pinned host operands, uploads / kernel / download overlapped across calls: same results."""
+    import torch
+    M, N, K = 512, 384, 256
+    pipe = ph.HostPipeline(torch, dev, [((M, K), torch.float32), ((K, N), torch.float32), ((M, N), torch.float32)],
+                           lambda a, b, c, stream: ph.gemm(a, b, c, 0.5, 1.5, ph.GEMM_FP32, stream=stream), result_index=2)
+    calls = []
+    for s in range(5):                      # more calls than buffer sets
+        a, b, c = _inputs(oracle, M, N, K, seeds=(10 * s + 1, 10 * s + 2, 10 * s + 3))
+        host = [torch.from_numpy(x).pin_memory() for x in (a, b, c)]
+        out = torch.empty((M, N), dtype=torch.float32).pin_memory()
+        pipe.submit(host, out)
+        calls.append((a, b, c, out))
+    pipe.join()
+    torch.cuda.synchronize()
+    assert ph.device_status() == 0
+    for a, b, c, out in calls:
+        assert oracle.rel_frobenius(out.numpy(), oracle.gemm_rows(a, b, c, 0.5, 1.5)) <= TOL_FP32
