@@ -399,6 +399,19 @@ PH_API int64_t phobos_autotune_super(const PhTuneResult *r, int32_t i, const cha
 PH_API void phobos_autotune_cost(const PhTuneResult *r, int32_t i, double *makespan, double *compute, double *comm,
                                  uint64_t *peak, uint64_t *fetch_bytes);
 
+/* ---- wire format of segments --------------------------------------------------------------- *
+ * `phobos.v1.Segment` (phobos-cluster/proto/v1/phobos_v1_isa.proto:93-113) to and from PhInstr
+ * records, without a protobuf runtime: segments a phobos scheduler emits can be issued to the
+ * executor, and segments planned here can be sent to a phobos pod.                            */
+typedef struct PhSegmentMsg PhSegmentMsg;
+PH_API PhSegmentMsg *phobos_segment_decode(const void *data, size_t n);   /* NULL on error */
+PH_API void phobos_segment_free(PhSegmentMsg *m);
+PH_API uint64_t phobos_segment_id(const PhSegmentMsg *m);
+PH_API int32_t phobos_segment_n_instrs(const PhSegmentMsg *m);
+PH_API const PhInstr *phobos_segment_instrs(const PhSegmentMsg *m);
+/* encoded size (written to `out` when `cap` suffices); SIZE_MAX on error */
+PH_API size_t phobos_segment_encode(uint64_t id, const PhInstr *instrs, int32_t n, void *out, size_t cap);
+
 #ifdef __cplusplus
 }
 #endif

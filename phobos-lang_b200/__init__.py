@@ -367,5 +367,5 @@ from .storage import load_region, storage_path, store_region  # noqa: E402
 from .executor import Executor, Instr  # noqa: E402
 from .partition import PartitionPlan, plan_partition  # noqa: E402
 from .hostpipe import HostPipeline  # noqa: E402
-from .planner import (DIRECT_LOAD, HOME_LOAD_PEER_FETCH, NO_BUDGET, Plan, Program, autotune, plan,  # noqa: E402
-                      run_plan)
+from .planner import (DIRECT_LOAD, HOME_LOAD_PEER_FETCH, NO_BUDGET, Plan, Program, autotune, decode_segment,  # noqa: E402
+                      encode_segment, plan, run_plan)

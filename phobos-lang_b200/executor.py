@@ -28,6 +28,37 @@ class Instr:
     _keep: list = field(default_factory=list, repr=False)
 
 
+def instr_array(instrs):
+    """[Instr, ...] -> (ctypes array of PhInstr, objects that must stay alive while the array is used)."""
+    from . import PhInstr, PhScalar, PhTileArg
+    arr = (PhInstr * max(1, len(instrs)))()
+    keep = [instrs]
+    for i, ins in enumerate(instrs):
+        a = arr[i]
+        a.iid, a.op, a.tile = ins.iid, ins.op, ins.tile
+        deps = (ctypes.c_uint64 * max(1, len(ins.deps)))(*ins.deps)
+        keep.append(deps)
+        a.deps, a.n_deps = deps, len(ins.deps)
+        a.data_type, a.shape_rank = ins.data_type, len(ins.shape)
+        for d, s in enumerate(ins.shape):
+            a.shape[d] = s
+        a.tensor = ins.tensor
+        a.region.rank = len(ins.region_shape)
+        for d, (o, s) in enumerate(zip(ins.region_offset, ins.region_shape)):
+            a.region.offset[d], a.region.shape[d] = o, s
+        a.from_node, a.kernel = ins.from_node, ins.kernel
+        args = (PhTileArg * max(1, len(ins.args)))(*[PhTileArg(t, m) for t, m in ins.args])
+        keep.append(args)
+        a.args, a.n_args = args, len(ins.args)
+        sc = (PhScalar * max(1, len(ins.scalars)))(*ins.scalars)
+        keep.append(sc)
+        a.scalars, a.n_scalars = sc, len(ins.scalars)
+        for d in range(3):
+            a.grid[d], a.cta[d] = ins.grid[d], ins.cta[d]
+        a.expected_serves = ins.expected_serves
+    return arr, keep
+
+
 class Executor:
     def __init__(self, device: int = 0, node_id: int = 0, arena_bytes: int = 512 << 20):
         from . import PH_ERR_DEVICE, PhobosError, last_error, lib
@@ -74,34 +105,9 @@ class Executor:
 
     def issue(self, instrs) -> None:
         """EngineMsg::Issue(Segment): adds the instructions and wires their dependency counters."""
-        from . import PhInstr, PhScalar, PhTileArg, check
-        instrs = list(instrs)
-        arr = (PhInstr * max(1, len(instrs)))()
-        keep = []
-        for i, ins in enumerate(instrs):
-            a = arr[i]
-            a.iid, a.op, a.tile = ins.iid, ins.op, ins.tile
-            deps = (ctypes.c_uint64 * max(1, len(ins.deps)))(*ins.deps)
-            keep.append(deps)
-            a.deps, a.n_deps = deps, len(ins.deps)
-            a.data_type, a.shape_rank = ins.data_type, len(ins.shape)
-            for d, s in enumerate(ins.shape):
-                a.shape[d] = s
-            a.tensor = ins.tensor
-            a.region.rank = len(ins.region_shape)
-            for d, (o, s) in enumerate(zip(ins.region_offset, ins.region_shape)):
-                a.region.offset[d], a.region.shape[d] = o, s
-            a.from_node, a.kernel = ins.from_node, ins.kernel
-            args = (PhTileArg * max(1, len(ins.args)))(*[PhTileArg(t, m) for t, m in ins.args])
-            keep.append(args)
-            a.args, a.n_args = args, len(ins.args)
-            sc = (PhScalar * max(1, len(ins.scalars)))(*ins.scalars)
-            keep.append(sc)
-            a.scalars, a.n_scalars = sc, len(ins.scalars)
-            for d in range(3):
-                a.grid[d], a.cta[d] = ins.grid[d], ins.cta[d]
-            a.expected_serves = ins.expected_serves
-        check(self._L.phobos_executor_issue(self._h, arr, len(instrs)))
+        from . import check
+        arr, keep = instr_array(list(instrs))
+        check(self._L.phobos_executor_issue(self._h, arr, len(keep[0])))
 
     def run(self) -> None:
         """Runs until nothing is pending; raises on the first failed instruction."""

@@ -147,25 +147,11 @@ class Plan:
 
     def segments(self, node: int):
         """[(segment id, [Instr, ...], peak bytes, incremental bytes), ...] in dispatch order."""
-        from . import PhInstr
-        from .executor import Instr
         out = []
         for s in range(self._L.phobos_plan_n_segments(self._h, node)):
             n = self._L.phobos_plan_segment_n_instrs(self._h, node, s)
             ptr = self._L.phobos_plan_segment_instrs(self._h, node, s)
-            arr = ctypes.cast(ptr, ctypes.POINTER(PhInstr)) if ptr else None
-            instrs = []
-            for i in range(n):
-                a = arr[i]
-                instrs.append(Instr(
-                    iid=int(a.iid), op=int(a.op), deps=tuple(int(a.deps[d]) for d in range(a.n_deps)), tile=int(a.tile),
-                    data_type=int(a.data_type), shape=tuple(int(a.shape[d]) for d in range(a.shape_rank)),
-                    tensor=int(a.tensor), region_offset=tuple(int(a.region.offset[d]) for d in range(a.region.rank)),
-                    region_shape=tuple(int(a.region.shape[d]) for d in range(a.region.rank)), from_node=int(a.from_node),
-                    kernel=int(a.kernel), args=tuple((int(a.args[j].tile), int(a.args[j].mode)) for j in range(a.n_args)),
-                    scalars=tuple(_copy_scalar(a.scalars[j]) for j in range(a.n_scalars)),
-                    grid=tuple(int(a.grid[d]) for d in range(3)), cta=tuple(int(a.cta[d]) for d in range(3)),
-                    expected_serves=int(a.expected_serves)))
+            instrs = _instrs_from_array(ptr, n)
             peak, inc = ctypes.c_uint64(), ctypes.c_uint64()
             self._L.phobos_plan_segment_mem(self._h, node, s, ctypes.byref(peak), ctypes.byref(inc))
             out.append((int(self._L.phobos_plan_segment_id(self._h, node, s)), instrs, peak.value, inc.value))
@@ -290,3 +276,66 @@ def run_plan(pl: Plan, program: Program, tensors, executors) -> None:
     for e in errors:
         if e is not None:
             raise e
+
+
+# ---- wire format of segments (phobos.v1.Segment) -----------------------------------------------------
+def _wire_sigs(L):
+    if getattr(L, "_wire_sigs", False):
+        return
+    c = ctypes
+    L.phobos_segment_decode.restype, L.phobos_segment_decode.argtypes = c.c_void_p, [c.c_char_p, c.c_size_t]
+    L.phobos_segment_free.restype, L.phobos_segment_free.argtypes = None, [c.c_void_p]
+    L.phobos_segment_id.restype, L.phobos_segment_id.argtypes = c.c_uint64, [c.c_void_p]
+    L.phobos_segment_n_instrs.restype, L.phobos_segment_n_instrs.argtypes = c.c_int32, [c.c_void_p]
+    L.phobos_segment_instrs.restype, L.phobos_segment_instrs.argtypes = c.c_void_p, [c.c_void_p]
+    L.phobos_segment_encode.restype = c.c_size_t
+    L.phobos_segment_encode.argtypes = [c.c_uint64, c.c_void_p, c.c_int32, c.c_void_p, c.c_size_t]
+    L._wire_sigs = True
+
+
+def _instrs_from_array(ptr, n):
+    from . import PhInstr
+    from .executor import Instr
+    arr = ctypes.cast(ptr, ctypes.POINTER(PhInstr)) if ptr else None
+    out = []
+    for i in range(n):
+        a = arr[i]
+        out.append(Instr(
+            iid=int(a.iid), op=int(a.op), deps=tuple(int(a.deps[d]) for d in range(a.n_deps)), tile=int(a.tile),
+            data_type=int(a.data_type), shape=tuple(int(a.shape[d]) for d in range(a.shape_rank)), tensor=int(a.tensor),
+            region_offset=tuple(int(a.region.offset[d]) for d in range(a.region.rank)),
+            region_shape=tuple(int(a.region.shape[d]) for d in range(a.region.rank)), from_node=int(a.from_node),
+            kernel=int(a.kernel), args=tuple((int(a.args[j].tile), int(a.args[j].mode)) for j in range(a.n_args)),
+            scalars=tuple(_copy_scalar(a.scalars[j]) for j in range(a.n_scalars)),
+            grid=tuple(int(a.grid[d]) for d in range(3)), cta=tuple(int(a.cta[d]) for d in range(3)),
+            expected_serves=int(a.expected_serves)))
+    return out
+
+
+def decode_segment(data: bytes):
+    """bytes of a phobos.v1.Segment -> (segment id, [Instr, ...])."""
+    from . import PH_ERR_PARSE, PhobosError, last_error, lib
+    L = lib()
+    _wire_sigs(L)
+    h = L.phobos_segment_decode(data, len(data))
+    if not h:
+        raise PhobosError(PH_ERR_PARSE, last_error())
+    try:
+        return int(L.phobos_segment_id(h)), _instrs_from_array(L.phobos_segment_instrs(h), L.phobos_segment_n_instrs(h))
+    finally:
+        L.phobos_segment_free(h)
+
+
+def encode_segment(seg_id: int, instrs) -> bytes:
+    """(segment id, [Instr, ...]) -> bytes of a phobos.v1.Segment."""
+    from . import PH_ERR_INVALID, PhobosError, last_error, lib
+    from .executor import instr_array
+    L = lib()
+    _wire_sigs(L)
+    arr, keep = instr_array(list(instrs))
+    n = L.phobos_segment_encode(seg_id, arr, len(keep[0]), None, 0)
+    if n == ctypes.c_size_t(-1).value:
+        raise PhobosError(PH_ERR_INVALID, last_error())
+    buf = ctypes.create_string_buffer(max(1, n))
+    L.phobos_segment_encode(seg_id, arr, len(keep[0]), buf, n)
+    return buf.raw[:n]

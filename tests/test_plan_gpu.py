@@ -132,3 +132,30 @@ scalar scale = f32 0.08838834764831845
     got = ph.load_region(f"file://{tmp_path}/o.tensor", (Nq, D), (0, 0), (Nq, D), dtype=ph.F16).astype(np.float32)
     want = oracle.flash_rows(q, k, v, 0.08838834764831845)
     assert oracle.rel_frobenius(got, want) <= 2e-3
+
+
+def test_segments_from_the_wire_run_on_the_executor(ph, oracle, dev, tmp_path):
+    """What a pod does with a phobos.v1.Segment message: decode, issue, run."""
+    M, N, K = 512, 512, 512
+    a = oracle.lcg_fill(1, M * K).reshape(M, K)
+    b = oracle.lcg_fill(2, K * N).reshape(K, N)
+    c = oracle.lcg_fill(3, M * N).reshape(M, N)
+    uris = [f"file://{tmp_path}/{n}.tensor" for n in "abc"]
+    for uri, x in zip(uris, (a, b, c)):
+        ph.store_region(uri, x.shape, (0, 0), x)
+    prog = ph.Program(GEMM_PH)
+    pl = ph.plan(prog, {"M": M, "N": N, "K": K}, budget=3 * 256 * 256 * 4,
+                 scalars={"alpha": ph.scalar_f32(0, -0.5), "beta": ph.scalar_f32(0, 0.25)})
+    messages = [ph.encode_segment(sid, instrs) for sid, instrs, _, _ in pl.segments(0)]
+    assert len(messages) > 1
+    with ph.Executor(0, 0, 8 << 20) as ex:
+        ex.set_tensors([(u, ph.F32, sh, md) for u, sh, md in zip(uris, ((M, K), (K, N), (M, N)), (ph.READ, ph.READ, ph.RMW))])
+        for k, entry in enumerate(prog.leaves):
+            ex.set_kernel(k, entry)
+        for m in messages:
+            _, instrs = ph.decode_segment(m)
+            ex.issue(instrs)
+        ex.run()
+        assert all(d[1] == 0 for d in ex.completions())
+    got = ph.load_region(uris[2], (M, N), (0, 0), (M, N))
+    assert oracle.rel_frobenius(got, oracle.gemm_rows(a, b, c, -0.5, 0.25)) <= 1e-5
