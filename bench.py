@@ -43,6 +43,7 @@ NCU_TRAFFIC_BYTES = {
     "gemm_fp16": 1_189_407_000 + 124_635_648,              # profiles/gemm_tc2_fp16_8192.md
     "flash_fp16": 402_703_360 + 110_934_528,               # profiles/flash_fwd_fp16_bh128_s4096_d128.md
     "matmul_cluster_fp32": 56_757_379_328 + 1_097_407_232,  # 16384^3 on one GPU, same file as gemm_fp32
+    "saxpy_fp32": 268_465_664 + 90_302_720,                 # profiles/saxpy_fp32_n2p25.md
 }
 
 
@@ -296,6 +297,62 @@ def bench_flash(ctx: Ctx, BH: int, S: int, D: int, peaks, cpu_baseline=True, e2e
     return out
 
 
+def bench_saxpy(ctx: Ctx, n: int, peaks, cpu_baseline=True, e2e=True):
+    """saxpy_fp32 at the reference bench's size (n = 2^25, alpha = 2, phobos-bench/src/main.rs:1198-1199):
+    12 bytes of HBM traffic per element, 2 flop."""
+    ph, torch, dev = ctx.ph, ctx.torch, ctx.dev
+    alpha = 2.0
+    sets = []
+    for s in range(2):     # two input sets: 768 MB in rotation, every launch reads from HBM
+        x, y = (torch.empty((n,), dtype=torch.float32, device=dev) for _ in range(2))
+        ph.fill_random(x, seed=42 + 2 * s)
+        ph.fill_random(y, seed=43 + 2 * s)
+        sets.append((x, y, torch.empty((n,), dtype=torch.float32, device=dev)))
+
+    def step(i):
+        x, y, o = sets[i % len(sets)]
+        ph.saxpy(x, y, o, alpha)
+
+    ms_total, ms_launch, ms_min = ctx.time_steps(step)
+    ph.device_status()
+    flops, nbytes = 2.0 * n, 12.0 * n
+    ach = nbytes / (ms_launch * 1e-3) / 1e9
+    out = {"workload": "saxpy_fp32", "n": n, "alpha": alpha, "tflops": flops / (ms_total * 1e-3) / 1e12,
+           "gbytes_per_s": nbytes / (ms_total * 1e-3) / 1e9, "ms_per_step": ms_total, "ms_per_launch": ms_launch,
+           "ms_min": ms_min, "input_sets": len(sets),
+           "roofline": {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
+                        "peak_source": f"of {peaks['_source']} (STREAM-style copy)", "traffic": NCU_TRAFFIC_BYTES.get("saxpy_fp32")}}
+    if e2e:
+        x, y, o = sets[0]
+        hx, hy = pinned_like(torch, x), pinned_like(torch, y)
+        ho = torch.empty(o.shape, dtype=o.dtype, device="cpu", pin_memory=True)
+        pipe = ph.HostPipeline(torch, dev, [(t.shape, t.dtype) for t in (x, y, o)],
+                               lambda a, b, c, stream: ph.saxpy(a, b, c, alpha, stream=stream), result_index=2)
+
+        def e2e_step(i):
+            pipe.submit((hx, hy, None), ho)
+
+        ms_e2e, _, _ = ctx.time_steps(e2e_step, steps=max(6, min(ctx.steps, 20)), warmup=3, finish=pipe.join)
+        del pipe
+        out["e2e"] = {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
+                      "h2d_bytes_per_step": 8 * n, "d2h_bytes_per_step": 4 * n}
+    if cpu_baseline:
+        import oracle
+        xh, yh = oracle.lcg_fill(42, n), oracle.lcg_fill(43, n)
+        reps, t0 = 0, time.time()
+        while True:
+            oracle.saxpy(xh, yh, alpha)
+            reps += 1
+            dt = time.time() - t0
+            if dt >= ctx.cpu_seconds or reps >= 64:
+                break
+        out["cpu_baseline"] = {"value": flops * reps / dt / 1e12, "unit": "TFLOP/s", "cores": oracle.threads(), "kind": "port",
+                               "sample": f"{reps} x (all {n} elements; f32 multiply then add, OpenMP); {dt:.2f} s"}
+    del sets
+    torch.cuda.empty_cache()
+    return out
+
+
 # ---------------------------------------------------------------------------------------------
 # CPU baseline: the oracle (port of the reference's f64 verifier arithmetic), bounded sample
 # ---------------------------------------------------------------------------------------------
@@ -536,6 +593,7 @@ def main():
         "flash_fp16": lambda: bench_flash(ctx, 128, 4096, 128, peaks, cpu),
         "matmul_cluster_fp32": lambda: bench_gemm(ctx, "matmul_cluster_fp32", 16384, 16384, 16384, 0.125, 1.5, peaks,
                                                   cpu_baseline=False, e2e=False),
+        "saxpy_fp32": lambda: bench_saxpy(ctx, 1 << 25, peaks, cpu),
     }
     head_name = args.only or "gemm_fp16tc_fp32acc"
     ctx.cpu_seconds = 10.0     # the headline's CPU baseline gets a sample of about ten seconds
@@ -553,9 +611,9 @@ def main():
     line = {"metric": metric, "value": head["tflops"], "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None,
-            "dtype": {"gemm_fp32": "f32", "matmul_cluster_fp32": "f32", "gemm_fp16": "f16"}.get(head_name, "f16 x f16 -> f32"),
+            "dtype": {"gemm_fp32": "f32", "matmul_cluster_fp32": "f32", "gemm_fp16": "f16", "saxpy_fp32": "f32"}.get(head_name, "f16 x f16 -> f32"),
             "data": "synthetic (seeded Lcg streams of phobos-base/src/rng.rs, generated on the device)",
-            "config": {"workload": head_name, **{k: head[k] for k in head if k in ("M", "N", "K", "alpha", "beta", "batch_heads", "seq_len", "head_dim")},
+            "config": {"workload": head_name, **{k: head[k] for k in head if k in ("M", "N", "K", "n", "alpha", "beta", "batch_heads", "seq_len", "head_dim")},
                        "l2": f"{head.get('input_sets', 1)} rotating input sets, working set larger than L2"},
             "roofline": head["roofline"], "cpu_baseline": head.get("cpu_baseline"), "e2e": head.get("e2e"),
             "gpu_launches": args.steps, "clocks": sampler.summary(ctx.windows), "suite": suite}

@@ -58,6 +58,8 @@ def lib() -> ctypes.CDLL:
         L.ph_oracle_flash_rows.restype = ctypes.c_int
         L.ph_oracle_flash_rows.argtypes = [ctypes.c_uint64] * 3 + [_f32p, _f32p, _f32p, ctypes.c_double, _u64p,
                                                                    ctypes.c_uint64, _f64p]
+        L.ph_oracle_saxpy.restype = None
+        L.ph_oracle_saxpy.argtypes = [_f32p, _f32p, ctypes.c_float, ctypes.c_uint64, _f32p]
         L.ph_oracle_rel_frobenius.restype = ctypes.c_double
         L.ph_oracle_rel_frobenius.argtypes = [_f32p, _f64p, ctypes.c_uint64]
         L.ph_oracle_max_rel_floor.restype = ctypes.c_double
@@ -164,6 +166,15 @@ def flash_rows(q, k, v, scale, rows=None) -> np.ndarray:
                                     _p(rows, _u64p), rows.size, _p(out, _f64p))
     if rc != 0:
         raise MemoryError("oracle flash")
+    return out
+
+
+def saxpy(x, y, alpha: float) -> np.ndarray:
+    """alpha * x + y in f32, product and sum rounded separately (verify_saxpy, main.rs:1179-1188)."""
+    x, y = _f32(x).ravel(), _f32(y).ravel()
+    assert x.size == y.size
+    out = np.empty(x.size, dtype=np.float32)
+    lib().ph_oracle_saxpy(_p(x, _f32p), _p(y, _f32p), alpha, x.size, _p(out, _f32p))
     return out
 
 

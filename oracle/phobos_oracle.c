@@ -370,6 +370,16 @@ PH_EXPORT int ph_oracle_flash_rows(uint64_t Nq, uint64_t Nk, uint64_t D, const f
 /* Error measures                                                      */
 /* ------------------------------------------------------------------ */
 /* ||got - want||_F / ||want||_F over n elements (the parity bar). */
+/* verify_saxpy (phobos-bench/src/main.rs:1179-1188): want[i] = alpha * x[i] + y[i] in f32, a
+ * rounded product and then a rounded sum (the volatile keeps the compiler from fusing them). */
+PH_EXPORT void ph_oracle_saxpy(const float *x, const float *y, float alpha, uint64_t n, float *out) {
+#pragma omp parallel for schedule(static)
+  for (uint64_t i = 0; i < n; i++) {
+    volatile float prod = alpha * x[i];
+    out[i] = prod + y[i];
+  }
+}
+
 PH_EXPORT double ph_oracle_rel_frobenius(const float *got, const double *want, uint64_t n) {
   double num = 0.0, den = 0.0;
 #pragma omp parallel for reduction(+ : num, den) schedule(static)

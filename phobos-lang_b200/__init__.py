@@ -97,6 +97,7 @@ def lib() -> ctypes.CDLL:
             "phobos_device_info": (c.c_int, [c.c_int, c.POINTER(PhDeviceInfo)]),
             "phobos_device_status": (c.c_int, [vp, c.POINTER(u32)]),
             "phobos_gemm": (c.c_int, [TP, TP, TP, f32, f32, i32, vp, sz, vp]),
+            "phobos_saxpy": (c.c_int, [TP, TP, TP, f32, vp]),
             "phobos_gemm_workspace_bytes": (sz, [i32, i32, i64, i64, i64]),
             "phobos_gemm_fp16tc_noalloc": (c.c_int, [TP, TP, TP, f32, f32, vp]),
             "phobos_matmul_init": (c.c_int, [TP, f32, i32, vp]),
@@ -249,6 +250,12 @@ def gemm_fp16tc_noalloc(A, B, C, alpha: float, beta: float, stream=None) -> None
     a, b, c = tensor_desc(A), tensor_desc(B), tensor_desc(C)
     check(lib().phobos_gemm_fp16tc_noalloc(ctypes.byref(a), ctypes.byref(b), ctypes.byref(c), alpha, beta,
                                            _stream_ptr(stream)))
+
+
+def saxpy(x, y, out, alpha: float, stream=None) -> None:
+    """out = alpha * x + y on rank-1 f32 tensors (examples/saxpy_fp32.ph; phobos-bench/src/main.rs:1190-1250)."""
+    dx, dy, do = tensor_desc(x), tensor_desc(y), tensor_desc(out)
+    check(lib().phobos_saxpy(ctypes.byref(dx), ctypes.byref(dy), ctypes.byref(do), alpha, _stream_ptr(stream)))
 
 
 def gemm_workspace_bytes(kind: int, a_dtype: int, M: int, N: int, K: int) -> int:

@@ -344,6 +344,38 @@ int phobos_flash_trace(uint64_t* device_buf, uint64_t n_words) {
 }
 
 // ---- launch by entry name ---------------------------------------------------------------
+// A rank-1 f32 vector view (saxpy): contiguous, 16-byte aligned.
+static int vector_of(const PhTensor* t, const char* name, float** base, long long* n) {
+  if (!t) return fail(PH_ERR_INVALID, "%s: null tensor descriptor", name);
+  if (!t->ptr) return fail(PH_ERR_INVALID, "%s: null data pointer", name);
+  if (t->rank != 1) return fail(PH_ERR_INVALID, "%s: rank %d, expected 1", name, t->rank);
+  if (t->dtype != PH_F32) return fail(PH_ERR_UNSUPPORTED, "%s: element type %d is not f32", name, t->dtype);
+  if (t->sizes[0] <= 0) return fail(PH_ERR_INVALID, "%s: empty extent", name);
+  if (t->strides[0] != 1) return fail(PH_ERR_INVALID, "%s: stride %lld, expected 1", name, (long long)t->strides[0]);
+  if (t->offset < 0) return fail(PH_ERR_INVALID, "%s: negative offset", name);
+  float* b = static_cast<float*>(t->ptr) + t->offset;
+  if (reinterpret_cast<uintptr_t>(b) % 16 != 0) return fail(PH_ERR_INVALID, "%s: data pointer is not 16-byte aligned", name);
+  *base = b;
+  *n = t->sizes[0];
+  return PH_OK;
+}
+
+int phobos_saxpy(const PhTensor* x, const PhTensor* y, const PhTensor* out, float alpha, void* stream) {
+  clear_error();
+  float *xp, *yp, *op;
+  long long nx, ny, no;
+  int rc;
+  if ((rc = vector_of(x, "x", &xp, &nx)) || (rc = vector_of(y, "y", &yp, &ny)) || (rc = vector_of(out, "out", &op, &no)))
+    return rc;
+  if (nx != ny || nx != no) return fail(PH_ERR_INVALID, "saxpy: extents differ (%lld, %lld, %lld)", nx, ny, no);
+  DeviceState* ds;
+  if ((rc = device_state(&ds))) return rc;
+  const char* err = "";
+  rc = launch_saxpy(xp, yp, op, static_cast<unsigned long long>(nx), alpha, ds->sm_count, static_cast<cudaStream_t>(stream),
+                    &err);
+  return map_launch_rc(rc, "saxpy", err);
+}
+
 // kind_hint: -1, or a PhGemmKind / PH_KIND_AUTO in the low byte, optionally | PH_LAUNCH_STEP_LEAF
 static bool hint_is_step(int32_t kind_hint) { return kind_hint >= 0 && (kind_hint & PH_LAUNCH_STEP_LEAF) != 0; }
 static int gemm_kind_from_types(const PhTensor* t, int32_t kind_hint) {
@@ -427,6 +459,13 @@ int phobos_launch(const char* entry, const PhTensor* t, int32_t n_tensors, const
     float scale;
     if ((rc = scalar_f32(scalars, n_scalars, 4, &scale))) return rc;
     return phobos_flash_attention(&t[0], &t[1], &t[2], &t[3], scale, 1, workspace, workspace_bytes, stream);
+  }
+  if (!strcmp(entry, "saxpy")) {
+    // saxpy(x, y, out, alpha): examples/saxpy_fp32.ph
+    if (n_tensors != 3) return fail(PH_ERR_INVALID, "saxpy takes 3 tensors, got %d", n_tensors);
+    float alpha;
+    if ((rc = scalar_f32(scalars, n_scalars, 3, &alpha))) return rc;
+    return phobos_saxpy(&t[0], &t[1], &t[2], alpha, stream);
   }
   return fail(PH_ERR_UNSUPPORTED, "no native kernel for entry '%s'", entry);
 }

@@ -47,6 +47,9 @@ int launch_fill_random_block(void* out, int dtype_is_f16, unsigned long long row
                              unsigned long long stream_pitch, float scale, cudaStream_t stream, const char** err);
 int launch_f32_to_f16(const float* in, void* out, unsigned long long n, cudaStream_t stream, const char** err);
 int launch_f16_to_f32(const void* in, float* out, unsigned long long n, cudaStream_t stream, const char** err);
+// out = alpha * x + y, one rounded multiply and one rounded add per element
+int launch_saxpy(const float* x, const float* y, float* out, unsigned long long n, float alpha, int sm_count,
+                 cudaStream_t stream, const char** err);
 // Strided 2-D f32 -> contiguous f16 (rows x cols), used to stage f32-stored tensor-core operands.
 int launch_f32_to_f16_2d(const float* in, long long ld_in, void* out, long long rows, long long cols,
                          cudaStream_t stream, const char** err);

@@ -195,7 +195,7 @@ def test_rejects_bad_descriptors(ph, dev):
         ph.gemm(A, torch.zeros(32, 64, device=dev), A, 1.0, 0.0, ph.GEMM_FP32)   # K mismatch
     assert e.value.code == ph.PH_ERR_INVALID
     with pytest.raises(ph.PhobosError) as e:
-        ph.launch("saxpy", [A], [])
+        ph.launch("kda", [A], [])
     assert e.value.code == ph.PH_ERR_UNSUPPORTED
 
 
@@ -246,3 +246,25 @@ def test_host_pipeline_matches_direct_calls(ph, oracle, dev):
     assert ph.device_status() == 0
     for a, b, c, out in calls:
         assert oracle.rel_frobenius(out.numpy(), oracle.gemm_rows(a, b, c, 0.5, 1.5)) <= TOL_FP32
+
+
+@pytest.mark.parametrize("n", [4, 1 << 10, (1 << 20) + 12, 1 << 25])
+def test_saxpy_bit_exact(ph, oracle, dev, n):
+    """out = alpha*x + y: bit-identical to the reference's own check (a rounded product, then a rounded sum),
+    at the reference bench's size 2^25 and at ragged sizes (tail after the unrolled main loop)."""
+    import torch
+    x, y = oracle.lcg_fill(42, n), oracle.lcg_fill(43, n)
+    X, Y = _to(dev, x), _to(dev, y)
+    O = torch.full((n,), float("nan"), dtype=torch.float32, device=dev)
+    ph.saxpy(X, Y, O, 2.0)
+    want = oracle.saxpy(x, y, 2.0)
+    assert np.array_equal(O.cpu().numpy().view(np.uint32), want.view(np.uint32))
+    # an alpha whose products need rounding separates mul+add from a fused multiply-add
+    ph.launch("saxpy", [X, Y, O], [ph.scalar_f32(3, 0.3)])
+    want = oracle.saxpy(x, y, 0.3)
+    assert np.array_equal(O.cpu().numpy().view(np.uint32), want.view(np.uint32))
+    fused = (np.float64(np.float32(0.3)) * x.astype(np.float64) + y.astype(np.float64)).astype(np.float32)
+    if n >= 1 << 10:
+        assert not np.array_equal(fused, want)
+    with pytest.raises(ph.PhobosError):
+        ph.saxpy(X, Y[: n - 4] if n > 4 else Y.reshape(2, 2), O, 1.0)

@@ -121,3 +121,11 @@ def test_normal_generator_statistics(oracle):
     x = oracle.lcg_fill_normal(4, 1 << 18)
     assert abs(float(x.mean())) < 0.01 and abs(float(x.std()) - 1.0) < 0.01
     assert np.array_equal(x[:101], oracle.lcg_fill_normal(4, 101))
+
+
+def test_saxpy_rounds_the_product_then_the_sum(oracle):
+    """verify_saxpy (phobos-bench/src/main.rs:1179-1188) against numpy's separately rounded f32 ops."""
+    x, y = oracle.lcg_fill(42, 100003), oracle.lcg_fill(43, 100003)
+    for alpha in (2.0, 0.3, -1.7):
+        want = (np.float32(alpha) * x) + y              # numpy rounds each f32 operation
+        assert np.array_equal(oracle.saxpy(x, y, alpha).view(np.uint32), want.view(np.uint32))
