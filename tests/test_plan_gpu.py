@@ -159,3 +159,44 @@ def test_segments_from_the_wire_run_on_the_executor(ph, oracle, dev, tmp_path):
         assert all(d[1] == 0 for d in ex.completions())
     got = ph.load_region(uris[2], (M, N), (0, 0), (M, N))
     assert oracle.rel_frobenius(got, oracle.gemm_rows(a, b, c, -0.5, 0.25)) <= 1e-5
+
+
+SAXPY_PH = """
+@cluster(CHUNK in [65536, 1048576])
+@autotune(CHUNK in [16, 8192])
+kernel saxpy(x: tensor<f32>[N], y: tensor<f32>[N], out: tensor<f32>[N], alpha: f32) {
+  let base = program_id(0) * CHUNK
+  out[base :+ CHUNK] = alpha * x[base :+ CHUNK] + y[base :+ CHUNK]
+}
+"""
+
+
+def test_rank1_job_planned_and_executed(ph, oracle, dev, tmp_path):
+    """An elementwise kernel over rank-1 tensors: one leaf per supertile, two nodes, bit-exact result."""
+    import torch
+    n = 4 * 65536
+    x, y = oracle.lcg_fill(42, n), oracle.lcg_fill(43, n)
+    for name, v in (("x", x), ("y", y), ("out", np.zeros(n, np.float32))):
+        ph.store_region(f"file://{tmp_path}/{name}.tensor", (n,), (0,), v)
+    job = ph.parse_job_text(f"""
+source = saxpy.ph
+dim N = {n}
+tensor x = read f32 {n} file://{tmp_path}/x.tensor
+tensor y = read f32 {n} file://{tmp_path}/y.tensor
+tensor out = write f32 {n} file://{tmp_path}/out.tensor
+scalar alpha = f32 0.3
+""", "job.txt", SAXPY_PH)
+    prog = ph.Program(job.source)
+    prog.check_job(job)
+    pl = ph.plan(prog, job.dims, nodes=2, scalars={"alpha": ph.PhScalar(0, job.scalars[0].dtype, job.scalars[0].bits)})
+    pl.validate()
+    assert len(pl.stores) == 4
+    ndev = torch.cuda.device_count()
+    exs = [ph.Executor(k if k < ndev else 0, k, 4 << 20) for k in range(2)]
+    try:
+        ph.run_plan(pl, prog, [(t.uri, t.dtype, t.shape, t.mode) for t in job.tensors], exs)
+    finally:
+        for ex in exs:
+            ex.close()
+    got = ph.load_region(f"file://{tmp_path}/out.tensor", (n,), (0,), (n,))
+    assert np.array_equal(got.view(np.uint32), oracle.saxpy(x, y, 0.3).view(np.uint32))
