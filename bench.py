@@ -452,6 +452,26 @@ def bench_partitioned(ctx: Ctx, world: int, rank: int, MNK: int, alpha: float, b
     ms = float(t.item())
     flops = gemm_flops(MNK, MNK, MNK)
 
+    # upper bound without any exchange (the reference's DirectLoad ingest: every rank holds the whole A row
+    # panel and B column panel it consumes): the same init + step leaves over resident panels
+    a_full = torch.empty((mb, MNK), dtype=torch.float32, device=dev)
+    b_full = torch.empty((MNK, nb), dtype=torch.float32, device=dev)
+    fill_block(ph, a_full, 1, row0, 0, MNK)
+    fill_block(ph, b_full, 2, 0, col0, MNK)
+
+    def direct_step(i):
+        c_block.copy_(c0)
+        leaf_init(c_block, beta)
+        for k0 in range(0, MNK, kc):
+            leaf_step(a_full[:, k0:k0 + kc], b_full[k0:k0 + kc, :], c_block, alpha)
+
+    ms_direct, _, _ = ctx.time_steps(direct_step, steps=max(2, min(ctx.steps, 3)), warmup=1, barrier=dist.barrier)
+    t = torch.tensor([ms_direct], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_direct = float(t.item())
+    del a_full, b_full
+    torch.cuda.empty_cache()
+
     # e2e: shards come from pinned host memory every step, the C block goes back
     hA, hB, hC = pinned_like(torch, a_shard), pinned_like(torch, b_shard), pinned_like(torch, c0)
     hOut = torch.empty(c0.shape, dtype=c0.dtype, device="cpu", pin_memory=True)
@@ -475,6 +495,8 @@ def bench_partitioned(ctx: Ctx, world: int, rank: int, MNK: int, alpha: float, b
            "grid": f"{plan.pr}x{plan.pc}", "k_chunk": kc, "steps_per_rank": len(plan.steps),
            "tflops": ach, "ms_per_step": ms,
            "peer_bytes_per_step": plan.total_peer_bytes(), "peer_bytes_per_rank": plan.recv_bytes(rank),
+           "direct_load_bound": {"tflops": flops / (ms_direct * 1e-3) / 1e12, "ms_per_step": ms_direct,
+                                 "note": "panels resident on every rank, no exchange: upper bound for the partitioned run"},
            "roofline": {"bound": "fp32_ffma", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
                         "peak_source": f"{world} x {info.sm_count} SMs x 128 lanes x 2 x {info.sm_clock_khz / 1e3:.0f} MHz",
                         "nvlink_floor_ms": plan.recv_bytes(rank) / 770e9 * 1e3, "traffic": None},
@@ -576,7 +598,8 @@ def main():
                                " broadcast over NVLink (NCCL) one step ahead of the step leaf",
                                "l2": "operands (1 GiB each) exceed L2"},
                     "roofline": res["roofline"], "e2e": {k: v for k, v in res["e2e"].items()},
-                    "gpu_launches": res["gpu_launches"], "peer_bytes_per_step": res["peer_bytes_per_step"]}
+                    "gpu_launches": res["gpu_launches"], "peer_bytes_per_step": res["peer_bytes_per_step"],
+                    "direct_load_bound": res["direct_load_bound"]}
         dist.barrier()
         sampler.stop()
         if rank == 0:

@@ -36,7 +36,8 @@ __global__ void __launch_bounds__(128, 1) umma_rate(int ts_mode, int N, int b_mn
   const int w = threadIdx.x >> 5;
   if (threadIdx.x == 0) tstart = clock64();
   __syncthreads();
-  if (whole_warp == 0 && (threadIdx.x & 31) == 0 && w < nissue) {
+  if ((whole_warp == 0 || whole_warp == 3) && (threadIdx.x & 31) == 0 && w < nissue) {
+    const int same = whole_warp == 3 ? 0 : 1;   // 0: every MMA reuses the first k-step's descriptors
     const uint32_t idesc = umma_idesc_f16(128, N, true, false, b_mn != 0);
     const uint32_t a = smem_u32(smem + w * 49152), b = smem_u32(smem + w * 49152 + 16384);
     const uint64_t ad0 = umma_smem_desc(a, 16, 1024);
@@ -50,8 +51,8 @@ __global__ void __launch_bounds__(128, 1) umma_rate(int ts_mode, int N, int b_mn
       for (int kk = 0; kk < 4; kk++) {
         // with nacc > 1 this one thread rotates over nacc independent accumulators
         const uint32_t dk = d + static_cast<uint32_t>((kk & (nacc - 1)) * N);  // nacc is a power of two
-        if (ts_mode) umma_f16_ts(dk, a_tmem + kk * 8, bd0 + kk * bstep, idesc, 1);
-        else umma_f16_ss(dk, ad0 + kk * 2, bd0 + kk * bstep, idesc, 1);
+        if (ts_mode) umma_f16_ts(dk, a_tmem + kk * 8 * same, bd0 + kk * bstep * same, idesc, 1);
+        else umma_f16_ss(dk, ad0 + kk * 2 * same, bd0 + kk * bstep * same, idesc, 1);
       }
     }
     out[4 + w] = clock64() - tstart;  // the issue loop alone, before the MMAs are known complete
@@ -61,7 +62,8 @@ __global__ void __launch_bounds__(128, 1) umma_rate(int ts_mode, int N, int b_mn
     }
     out[w] = clock64() - tstart;
   }
-  if (whole_warp != 0 && w < nissue) {
+  if ((whole_warp == 1 || whole_warp == 2) && w < nissue) {
+    const int same = whole_warp == 2 ? 0 : 1;
     // every lane runs the loop and the descriptor arithmetic (warp-uniform values);
     // only the tcgen05.mma itself is predicated on one elected lane
     const uint32_t idesc = umma_idesc_f16(128, N, true, false, b_mn != 0);
@@ -76,8 +78,8 @@ __global__ void __launch_bounds__(128, 1) umma_rate(int ts_mode, int N, int b_mn
 #pragma unroll
       for (int kk = 0; kk < 4; kk++) {
         if (elect_one()) {
-          if (ts_mode) umma_f16_ts(d, a_tmem + kk * 8, bd0 + kk * bstep, idesc, 1);
-          else umma_f16_ss(d, ad0 + kk * 2, bd0 + kk * bstep, idesc, 1);
+          if (ts_mode) umma_f16_ts(d, a_tmem + kk * 8 * same, bd0 + kk * bstep * same, idesc, 1);
+          else umma_f16_ss(d, ad0 + kk * 2 * same, bd0 + kk * bstep * same, idesc, 1);
         }
       }
     }
@@ -186,6 +188,19 @@ int main() {
     long long mx = h[0] > h[1] ? h[0] : h[1];
     printf("  A from %s, N=%3d, %d issuer(s): %6.1f clk/MMA complete, %6.1f clk/MMA to issue  (ideal %3d)%s\n",
            c[0] ? "TMEM" : "smem", c[1], c[2], static_cast<double>(mx) / (iters * 4 * c[2]),
+           static_cast<double>(h[4]) / (iters * 4), c[1] / 2, e == cudaSuccess ? "" : "  CUDA ERROR");
+  }
+  printf("every MMA with the same descriptors (no descriptor change between MMAs)\n");
+  const int sd[][3] = {{0, 128, 2}, {0, 128, 3}, {1, 128, 2}, {1, 128, 3}, {0, 64, 2}, {0, 256, 2}};
+  for (auto& c : sd) {
+    const int iters = 256;
+    cudaMemset(d, 0, 64);
+    umma_rate<<<148, 128, 200 * 1024>>>(c[0], c[1], 1, 1, 1, c[2], iters, d);
+    cudaError_t e = cudaDeviceSynchronize();
+    long long h[8];
+    cudaMemcpy(h, d, 64, cudaMemcpyDeviceToHost);
+    printf("  A from %s, N=%3d, %s: %6.1f clk/MMA complete, %6.1f clk/MMA to issue  (ideal %3d)%s\n", c[0] ? "TMEM" : "smem",
+           c[1], c[2] == 2 ? "whole warp" : "one lane  ", static_cast<double>(h[0]) / (iters * 4),
            static_cast<double>(h[4]) / (iters * 4), c[1] / 2, e == cudaSuccess ? "" : "  CUDA ERROR");
   }
   float* f;
