@@ -36,7 +36,19 @@ __global__ void __launch_bounds__(128, 1) umma_rate(int ts_mode, int N, int b_mn
   const int w = threadIdx.x >> 5;
   if (threadIdx.x == 0) tstart = clock64();
   __syncthreads();
-  if ((whole_warp == 0 || whole_warp == 3) && (threadIdx.x & 31) == 0 && w < nissue) {
+  __shared__ volatile int stop_flag;
+  if (threadIdx.x == 0) stop_flag = 0;
+  __syncthreads();
+  if (whole_warp == 4 && w >= nissue) {
+    // the other warps keep their schedulers busy with dependent FMAs until the issuer is done
+    float v = static_cast<float>(threadIdx.x);
+    while (stop_flag == 0) {
+#pragma unroll
+      for (int i = 0; i < 64; i++) v = fmaf(v, 1.0001f, 0.5f);
+    }
+    if (v == 12345.678f) out[7] = 1;
+  }
+  if ((whole_warp == 0 || whole_warp == 3 || whole_warp == 4) && (threadIdx.x & 31) == 0 && w < nissue) {
     const int same = whole_warp == 3 ? 0 : 1;   // 0: every MMA reuses the first k-step's descriptors
     const uint32_t idesc = umma_idesc_f16(128, N, true, false, b_mn != 0);
     const uint32_t a = smem_u32(smem + w * 49152), b = smem_u32(smem + w * 49152 + 16384);
@@ -61,6 +73,7 @@ __global__ void __launch_bounds__(128, 1) umma_rate(int ts_mode, int N, int b_mn
     while (!mbar_try_wait(&bar[w], 0) && ++spins < (1u << 26)) {
     }
     out[w] = clock64() - tstart;
+    stop_flag = 1;
   }
   if ((whole_warp == 1 || whole_warp == 2) && w < nissue) {
     const int same = whole_warp == 2 ? 0 : 1;
@@ -202,6 +215,18 @@ int main() {
     printf("  A from %s, N=%3d, %s: %6.1f clk/MMA complete, %6.1f clk/MMA to issue  (ideal %3d)%s\n", c[0] ? "TMEM" : "smem",
            c[1], c[2] == 2 ? "whole warp" : "one lane  ", static_cast<double>(h[0]) / (iters * 4),
            static_cast<double>(h[4]) / (iters * 4), c[1] / 2, e == cudaSuccess ? "" : "  CUDA ERROR");
+  }
+  printf("one issuing lane while the CTA's other three warps run dependent FMAs\n");
+  const int bz[][2] = {{0, 64}, {0, 128}, {0, 256}, {1, 128}, {1, 256}};
+  for (auto& c : bz) {
+    const int iters = 256;
+    cudaMemset(d, 0, 64);
+    umma_rate<<<148, 128, 200 * 1024>>>(c[0], c[1], 1, 1, 1, 4, iters, d);
+    cudaError_t e = cudaDeviceSynchronize();
+    long long h[8];
+    cudaMemcpy(h, d, 64, cudaMemcpyDeviceToHost);
+    printf("  A from %s, N=%3d: %6.1f clk/MMA complete  (ideal %3d)%s\n", c[0] ? "TMEM" : "smem", c[1],
+           static_cast<double>(h[0]) / (iters * 4), c[1] / 2, e == cudaSuccess ? "" : "  CUDA ERROR");
   }
   float* f;
   cudaMalloc(&f, 4);
