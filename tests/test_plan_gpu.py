@@ -200,3 +200,45 @@ scalar alpha = f32 0.3
             ex.close()
     got = ph.load_region(f"file://{tmp_path}/out.tensor", (n,), (0,), (n,))
     assert np.array_equal(got.view(np.uint32), oracle.saxpy(x, y, 0.3).view(np.uint32))
+
+
+def test_recovery_plan_redoes_a_dead_nodes_outputs(ph, oracle, dev, tmp_path):
+    """Node 1 of two never runs (the failure is made on the host: its segments are simply not issued).
+    The recovery plan re-runs its C supertiles on node 0 with fresh instruction ids and bumped tile
+    versions, next to what node 0 already did (phobos-sched/src/lib.rs:172-234)."""
+    M, N, K = 512, 512, 256
+    a = oracle.lcg_fill(1, M * K).reshape(M, K)
+    b = oracle.lcg_fill(2, K * N).reshape(K, N)
+    c = oracle.lcg_fill(3, M * N).reshape(M, N)
+    uris = [f"file://{tmp_path}/{n}.tensor" for n in "abc"]
+    for uri, x in zip(uris, (a, b, c)):
+        ph.store_region(uri, x.shape, (0, 0), x)
+    prog = ph.Program(GEMM_PH)
+    dims = {"M": M, "N": N, "K": K}
+    scalars = {"alpha": ph.scalar_f32(0, 2.0), "beta": ph.scalar_f32(0, -0.5)}
+    base = ph.plan(prog, dims, nodes=2, scalars=scalars)
+    tensors = [(u, ph.F32, sh, md) for u, sh, md in zip(uris, ((M, K), (K, N), (M, N)), (ph.READ, ph.READ, ph.RMW))]
+    with ph.Executor(0, 0, 8 << 20) as ex:
+        ex.set_tensors(tensors)
+        for k, entry in enumerate(prog.leaves):
+            ex.set_kernel(k, entry)
+        ex.issue(base.node_instrs(0))
+        ex.run()
+        done = {d[0] for d in ex.completions() if d[1] == 0}
+        durable = [(t, lin) for iid, node, t, lin in base.stores if node == 0 and iid in done]
+        assert len(durable) == 2
+        # half of C is still the original: node 1's supertiles were never computed
+        half = ph.load_region(uris[2], (M, N), (0, 0), (M, N))
+        want = oracle.gemm_rows(a, b, c, 2.0, -0.5).reshape(M, N)
+        lost = [(lin // 2, lin % 2) for _, node, _, lin in base.stores if node == 1]
+        for i, j in lost:
+            assert np.array_equal(half[i * 256:(i + 1) * 256, j * 256:(j + 1) * 256], c[i * 256:(i + 1) * 256, j * 256:(j + 1) * 256])
+        rec = ph.plan(prog, dims, nodes=2, scalars=scalars,
+                      recover={"dead": [1], "durable": durable, "version": 1, "iid_base": base.max_iid})
+        rec.validate()
+        assert sorted(lin for _, _, _, lin in rec.stores) == sorted(lin for _, node, _, lin in base.stores if node == 1)
+        ex.issue(rec.node_instrs(0))
+        ex.run()
+        assert all(d[1] == 0 for d in ex.completions()) and ex.arena_used == 0
+    got = ph.load_region(uris[2], (M, N), (0, 0), (M, N))
+    assert oracle.rel_frobenius(got, want) <= 1e-5
