@@ -9,16 +9,21 @@
 // per-element operation order, so on the same inputs the result is bit-identical
 // to a sequential f32 fma chain.
 //
-// Structure: CTA tile 128x128, K step 16, 256 threads, 8x8 outputs per thread in
-// registers.  A [128 x 16] and B [16 x 128] tiles are staged by TMA into a ring
-// of shared-memory stages; a `full` mbarrier per stage signals arrival and an
-// `empty` mbarrier (one arrival per warp) lets the refill proceed without a
-// CTA-wide barrier, so warps drift apart by up to a stage.  Fragments are read
-// with 128-bit shared loads; the A tile is stored 64B-swizzled so that the four
-// rows a warp reads in one instruction land in different banks.  The
-// multiply-adds are issued as packed fma.rn.f32x2 (two independent IEEE fmas per
-// instruction): the math is unchanged while the instruction count halves, which
-// moves the limit from the issue slots to the FMA pipe.  Two CTAs per SM.
+// Structure: CTA tile 128x128, K step 16, 128 threads, 8 rows x 16 columns of outputs per
+// thread in registers (128 accumulators as 64 packed pairs), two CTAs per SM.  A [128 x 16]
+// and B [16 x 128] tiles are staged by TMA into a ring of shared-memory stages; a `full`
+// mbarrier per stage signals arrival and an `empty` mbarrier (one arrival per warp) lets the
+// refill proceed without a CTA-wide barrier, so warps drift apart by up to a stage.  The A
+// tile is stored 64B-swizzled so that the rows a warp reads in one instruction land in
+// different banks.  The multiply-adds are issued as packed fma.rn.f32x2 (two independent
+// IEEE fmas per instruction): the math is unchanged while the instruction count halves.
+//
+// Why 8 x 16 per thread: a shared-memory wavefront delivers 4 bytes per lane, so a thread
+// tile of r x c outputs needs r + c wavefronts per k for r * c fmas.  The SM does 128 fmas
+// and 1 wavefront per clock, i.e. 4 fmas per lane per wavefront at balance: an 8 x 8 tile
+// sits exactly on that line (measured: 540 M shared wavefronts, the load pipe as busy as
+// the FMA pipe, 48 TFLOP/s), 8 x 16 needs 24 wavefronts per 128 fmas (75 %; 52 TFLOP/s).
+// The price is 255 registers per thread, hence two warps per scheduler.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -29,7 +34,7 @@ namespace {
 
 constexpr int BM = 128, BN = 128, BK = 16;
 constexpr int STAGES = 4;
-constexpr int THREADS = 256;
+constexpr int THREADS = 128;
 constexpr int A_BYTES = BM * BK * 4;  // 8 KB
 constexpr int B_BYTES = BK * BN * 4;  // 8 KB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -84,10 +89,10 @@ gemm_f32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
-  // warp tile 32 rows x 64 cols; warps arranged 4 (rows) x 2 (cols)
-  const int wrow = (warp >> 1) * 32, wcol = (warp & 1) * 64;
-  const int ty = lane >> 3;  // 0..3 : rows  wrow + ty + 4*i
-  const int tx = lane & 7;   // 0..7 : cols  wcol + tx*4 + 32*j + (0..3)
+  // warp tile 64 rows x 64 cols; warps arranged 2 (rows) x 2 (cols); 8 rows x 16 columns per thread
+  const int wrow = (warp >> 1) * 64, wcol = (warp & 1) * 64;
+  const int ty = lane >> 2;  // 0..7 : rows  wrow + ty + 8*i
+  const int tx = lane & 3;   // 0..3 : cols  wcol + tx*4 + 16*j + (0..3)
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; s++) {
@@ -111,12 +116,12 @@ gemm_f32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     for (int s = 0; s < STAGES && s < num_kb; s++) issue(s, s);
   }
 
-  // acc[i][jp]: row wrow + ty + 4*i, column pair jp (columns 2*jp, 2*jp+1 of the thread's 8)
-  unsigned long long acc[8][4];
+  // acc[i][jp]: row wrow + ty + 8*i, column pair jp (columns 2*jp, 2*jp+1 of the thread's 16)
+  unsigned long long acc[8][8];
 #pragma unroll
   for (int i = 0; i < 8; i++)
 #pragma unroll
-    for (int jp = 0; jp < 4; jp++) acc[i][jp] = 0ull;  // two +0.0f
+    for (int jp = 0; jp < 8; jp++) acc[i][jp] = 0ull;  // two +0.0f
 
   // byte offset of row (wrow + ty + 4*i) in an A tile and its swizzle term:
   // row r lives at r*64 B, its 16-byte chunk c at chunk (c ^ ((r >> 1) & 3))  (TMA 64B swizzle)
@@ -140,26 +145,30 @@ gemm_f32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const uint8_t* sA = smem + stage * STAGE_BYTES;
     const uint8_t* sB = smem + stage * STAGE_BYTES + A_BYTES;
 #pragma unroll
-    for (int kc = 0; kc < BK / 4; kc++) {
-      float4 a[8];
+    for (int k2 = 0; k2 < BK / 2; k2++) {
+      // two k at a time: a 64-bit load per row (rows of a warp sit in different banks thanks to
+      // the swizzle), four 128-bit loads of B per k
+      const int kc = k2 >> 1, half = k2 & 1;
+      float2 a[8];
 #pragma unroll
       for (int i = 0; i < 8; i++) {
-        const int r = wrow + ty + 4 * i;
-        a[i] = *reinterpret_cast<const float4*>(sA + a_row_base + i * 256 + ((kc ^ ((r >> 1) & 3)) << 4));
+        const int r = wrow + ty + 8 * i;
+        a[i] = *reinterpret_cast<const float2*>(sA + a_row_base + i * 512 + ((kc ^ ((r >> 1) & 3)) << 4) + half * 8);
       }
 #pragma unroll
-      for (int kk = 0; kk < 4; kk++) {
-        const uint8_t* brow = sB + (kc * 4 + kk) * (BN * 4) + b_col_base;
-        const ulonglong2 b01 = *reinterpret_cast<const ulonglong2*>(brow);
-        const ulonglong2 b23 = *reinterpret_cast<const ulonglong2*>(brow + 128);
+      for (int kk = 0; kk < 2; kk++) {
+        const uint8_t* brow = sB + (k2 * 2 + kk) * (BN * 4) + b_col_base;
+        ulonglong2 b[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) b[j] = *reinterpret_cast<const ulonglong2*>(brow + j * 64);
 #pragma unroll
         for (int i = 0; i < 8; i++) {
-          const float av = kk == 0 ? a[i].x : kk == 1 ? a[i].y : kk == 2 ? a[i].z : a[i].w;
-          const unsigned long long a2 = dup2(av);
-          ffma2(acc[i][0], a2, b01.x);
-          ffma2(acc[i][1], a2, b01.y);
-          ffma2(acc[i][2], a2, b23.x);
-          ffma2(acc[i][3], a2, b23.y);
+          const unsigned long long a2 = dup2(kk == 0 ? a[i].x : a[i].y);
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            ffma2(acc[i][2 * j], a2, b[j].x);
+            ffma2(acc[i][2 * j + 1], a2, b[j].y);
+          }
         }
       }
     }
@@ -175,12 +184,12 @@ gemm_f32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   if (ok) {
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-      const int row = mb * BM + wrow + ty + 4 * i;
+      const int row = mb * BM + wrow + ty + 8 * i;
       if (row < p.M) {
         float* crow = p.C + static_cast<long long>(row) * p.ldc;
 #pragma unroll
-        for (int j = 0; j < 2; j++) {
-          const int col = nb * BN + wcol + tx * 4 + 32 * j;
+        for (int j = 0; j < 4; j++) {
+          const int col = nb * BN + wcol + tx * 4 + 16 * j;
           if (col < p.N) {  // N is a multiple of 4
             const float4 old = *reinterpret_cast<const float4*>(crow + col);
             const float2 lo = unpack2(acc[i][2 * j]), hi = unpack2(acc[i][2 * j + 1]);
