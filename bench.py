@@ -429,10 +429,17 @@ def bench_partitioned(ctx: Ctx, world: int, rank: int, MNK: int, alpha: float, b
     comm, comp = torch.cuda.Stream(), torch.cuda.Stream()
     bufs = part.alloc_buffers(plan, a_shard, b_shard)
     leaf_init, leaf_step = part.cuda_leaves()
+    # exchange: peer copies out of the home ranks' shards (no collective, no SMs); PHOBOS_EXCHANGE=nccl
+    # selects the broadcast form instead
+    peers, exchange = None, "nccl"
+    if os.environ.get("PHOBOS_EXCHANGE", "p2p") == "p2p":
+        peers = part.PeerShards(plan, rank, a_shard, b_shard)
+        exchange = "p2p"
+    pa, pb = (peers.a, peers.b) if peers is not None else (a_shard, b_shard)
 
     def step(i):
-        part.run_partitioned(plan, rank, a_shard, b_shard, c_block, alpha, beta, leaf_init, leaf_step, row_pg, col_pg,
-                             comm_stream=comm, compute_stream=comp, buffers=bufs)
+        part.run_partitioned(plan, rank, pa, pb, c_block, alpha, beta, leaf_init, leaf_step, row_pg, col_pg,
+                             comm_stream=comm, compute_stream=comp, buffers=bufs, peers=peers)
         torch.cuda.current_stream().wait_stream(comp)
         torch.cuda.current_stream().wait_stream(comm)
 
@@ -477,11 +484,16 @@ def bench_partitioned(ctx: Ctx, world: int, rank: int, MNK: int, alpha: float, b
     hOut = torch.empty(c0.shape, dtype=c0.dtype, device="cpu", pin_memory=True)
 
     def e2e_step(i):
+        # the uploaded shards are exchanged by broadcast here: a collective orders every rank's upload
+        # before its peers read it, which the one-sided copies of the timed path do not need
         a_shard.copy_(hA, non_blocking=True)
         b_shard.copy_(hB, non_blocking=True)
         c_block.copy_(hC, non_blocking=True)
         comp.wait_stream(torch.cuda.current_stream())
-        step(i)
+        part.run_partitioned(plan, rank, a_shard, b_shard, c_block, alpha, beta, leaf_init, leaf_step, row_pg, col_pg,
+                             comm_stream=comm, compute_stream=comp, buffers=bufs)
+        torch.cuda.current_stream().wait_stream(comp)
+        torch.cuda.current_stream().wait_stream(comm)
         hOut.copy_(c_block, non_blocking=True)
 
     ms_e2e, _, _ = ctx.time_steps(e2e_step, steps=max(3, min(ctx.steps, 5)), warmup=3, barrier=dist.barrier)
@@ -492,7 +504,7 @@ def bench_partitioned(ctx: Ctx, world: int, rank: int, MNK: int, alpha: float, b
     peak = info.fp32_peak_flops / 1e12 * world
     ach = flops / (ms * 1e-3) / 1e12
     out = {"workload": "matmul_cluster_fp32", "M": MNK, "N": MNK, "K": MNK, "alpha": alpha, "beta": beta,
-           "grid": f"{plan.pr}x{plan.pc}", "k_chunk": kc, "steps_per_rank": len(plan.steps),
+           "grid": f"{plan.pr}x{plan.pc}", "k_chunk": kc, "steps_per_rank": len(plan.steps), "exchange": exchange,
            "tflops": ach, "ms_per_step": ms,
            "peer_bytes_per_step": plan.total_peer_bytes(), "peer_bytes_per_rank": plan.recv_bytes(rank),
            "direct_load_bound": {"tflops": flops / (ms_direct * 1e-3) / 1e12, "ms_per_step": ms_direct,
@@ -595,7 +607,9 @@ def main():
                     "data": "synthetic (seeded Lcg streams of phobos-base/src/rng.rs, generated on the device)",
                     "config": {"workload": "matmul_cluster_fp32", "M": 16384, "N": 16384, "K": 16384, "alpha": 0.125,
                                "beta": 1.5, "parallelism": f"2-D C partition {res['grid']}, K chunks of {res['k_chunk']}"
-                               " broadcast over NVLink (NCCL) one step ahead of the step leaf",
+                               " copied over NVLink one step ahead of the step leaf ("
+                               + ("peer copies out of the home ranks' shards, no collective" if res["exchange"] == "p2p"
+                                  else "NCCL broadcast") + ")",
                                "l2": "operands (1 GiB each) exceed L2"},
                     "roofline": res["roofline"], "e2e": {k: v for k, v in res["e2e"].items()},
                     "gpu_launches": res["gpu_launches"], "peer_bytes_per_step": res["peer_bytes_per_step"],

@@ -151,14 +151,17 @@ def shard_inputs(plan: PartitionPlan, rank: int, A, B, C):
 
 def run_partitioned(plan: PartitionPlan, rank: int, a_shard, b_shard, c_block, alpha: float, beta: float,
                     leaf_init, leaf_step, row_pg=None, col_pg=None, comm_stream=None, compute_stream=None,
-                    buffers=None):
+                    buffers=None, peers=None):
     """Runs init + the chain of step leaves on this rank; c_block is updated in place.
 
     leaf_init(C, beta) and leaf_step(A_chunk, B_chunk, C, alpha) are the leaves
     (`matmul_init`, and `matmul` with beta = 1).  row_pg / col_pg are the process
     groups of the rank's grid row / column (None when the group has one member).
     With CUDA tensors the broadcasts of step t+1 run on `comm_stream` while the
-    leaf of step t runs on `compute_stream`.
+    leaf of step t runs on `compute_stream`.  With `peers` (a PeerShards) there is no
+    collective at all: every rank copies the chunks it is not home to straight out of the
+    home rank's shard (device-to-device copies over NVLink on `comm_stream`), and a_shard /
+    b_shard must be the tensors PeerShards holds.
     """
     import torch
     import torch.distributed as dist
@@ -183,13 +186,20 @@ def run_partitioned(plan: PartitionPlan, rank: int, a_shard, b_shard, c_block, a
         with ctx:
             if cuda and i >= 2 and consumed[i - 2] is not None:
                 comm_stream.wait_event(consumed[i - 2])   # buffer (i % 2) is free again
-            if plan.pc > 1:
+            if peers is not None:
+                if plan.pc > 1 and not a_local:
+                    a_src = a_buf[i % 2]
+                    a_src.copy_(peers.a_chunk(plan.rank_of(r, st.a_home_col), st.a_local_chunk), non_blocking=True)
+                if plan.pr > 1 and not b_local:
+                    b_src = b_buf[i % 2]
+                    b_src.copy_(peers.b_rows(plan.rank_of(st.b_home_row, c), st.b_local_row0, st.kc), non_blocking=True)
+            elif plan.pc > 1:
                 if a_local:
                     dist.broadcast(a_src, src=plan.rank_of(r, st.a_home_col), group=row_pg)
                 else:
                     a_src = a_buf[i % 2]
                     dist.broadcast(a_src, src=plan.rank_of(r, st.a_home_col), group=row_pg)
-            if plan.pr > 1:
+            if peers is None and plan.pr > 1:
                 if b_local:
                     dist.broadcast(b_src, src=plan.rank_of(st.b_home_row, c), group=col_pg)
                 else:
@@ -219,6 +229,46 @@ def run_partitioned(plan: PartitionPlan, rank: int, a_shard, b_shard, c_block, a
                 ev.record(compute_stream)
                 consumed[i] = ev
     return c_block
+
+
+class PeerShards:
+    """The home shards of all ranks, readable from every rank of the box.
+
+    Each rank puts its A and B home shards into symmetric memory (same shape on every rank, mapped into
+    every process over NVLink); `a_chunk` / `b_rows` return a view of another rank's shard that a plain
+    device-to-device copy can read.  The shards are inputs and never change during a run, so readers
+    need no handshake beyond the one barrier after they are filled.
+    """
+
+    def __init__(self, plan: PartitionPlan, rank: int, a_shard, b_shard):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        self.plan = plan
+        self.a_shape, self.b_shape = tuple(a_shard.shape), tuple(b_shard.shape)
+        self.dtype = a_shard.dtype
+        self.a = symm.empty(self.a_shape, dtype=a_shard.dtype, device=a_shard.device)
+        self.b = symm.empty(self.b_shape, dtype=b_shard.dtype, device=b_shard.device)
+        self.a.copy_(a_shard)
+        self.b.copy_(b_shard)
+        self._ha = symm.rendezvous(self.a, dist.group.WORLD)
+        self._hb = symm.rendezvous(self.b, dist.group.WORLD)
+        self._views = {}
+        import torch
+        torch.cuda.synchronize()
+        dist.barrier()                 # every shard is filled before anyone reads one
+
+    def _peer(self, which: str, peer_rank: int):
+        key = (which, peer_rank)
+        if key not in self._views:
+            h, shape = (self._ha, self.a_shape) if which == "a" else (self._hb, self.b_shape)
+            self._views[key] = h.get_buffer(peer_rank, shape, self.dtype)
+        return self._views[key]
+
+    def a_chunk(self, peer_rank: int, chunk: int):
+        return self._peer("a", peer_rank)[chunk]
+
+    def b_rows(self, peer_rank: int, row0: int, rows: int):
+        return self._peer("b", peer_rank)[row0:row0 + rows]
 
 
 def alloc_buffers(plan: PartitionPlan, a_shard, b_shard):
