@@ -168,6 +168,13 @@ PH_API size_t phobos_flash_workspace_bytes(int32_t dtype, int64_t batch_heads, i
  * -DPH_FLASH_TRACE carry the stamps; others return PH_ERR_UNSUPPORTED.        */
 PH_API int phobos_flash_trace(uint64_t *device_buf, uint64_t n_words);
 
+/* ---- kda (chunkwise gated linear attention) ------------------------------------------- *
+ * One head: Q, K, V, O [N, 64] f32, G [N, 1] the per-token log forget-gate, scale on the
+ * queries (examples/kda_fp32.ph:20-65; builtins cumsum / tril / transpose, SPEC.md).  A single
+ * program, as the kernel has no program_id: state S [64, 64] carried over chunks of 64 tokens. */
+PH_API int phobos_kda(const PhTensor *Q, const PhTensor *K, const PhTensor *V, const PhTensor *G, const PhTensor *O,
+                      float scale, void *stream);
+
 /* ---- saxpy ------------------------------------------------------------------------- *
  * out = alpha * x + y on rank-1 f32 tensors (examples/saxpy_fp32.ph:1-5; launch shape of
  * phobos-bench/src/main.rs:1222-1236).  A rounded multiply, then a rounded add, as the
@@ -178,7 +185,7 @@ PH_API int phobos_saxpy(const PhTensor *x, const PhTensor *y, const PhTensor *ou
  * The COMPUTE operand model: Op::Compute{kernel, args, scalars, grid, cta}
  * (phobos-cluster/src/isa.rs:38-44).  `entry` is the PTX entry name the
  * reference would look up (= kernel name, phobos-lang/src/codegen/kernel.rs:90-93):
- * "gemm", "matmul", "matmul_init", "flash_attention", "saxpy".  Tensors are in
+ * "gemm", "matmul", "matmul_init", "flash_attention", "saxpy", "kda".  Tensors are in
  * signature order; scalars carry their parameter position.  `grid` and `cta`
  * describe the reference's own device tiling and are validated for presence
  * only.  The GEMM regime follows from the element types unless `kind_hint`

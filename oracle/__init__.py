@@ -58,6 +58,9 @@ def lib() -> ctypes.CDLL:
         L.ph_oracle_flash_rows.restype = ctypes.c_int
         L.ph_oracle_flash_rows.argtypes = [ctypes.c_uint64] * 3 + [_f32p, _f32p, _f32p, ctypes.c_double, _u64p,
                                                                    ctypes.c_uint64, _f64p]
+        for fn, extra in ((L.ph_oracle_kda_recurrence, []), (L.ph_oracle_kda_chunked, [ctypes.c_uint64])):
+            fn.restype = None
+            fn.argtypes = [_f32p, _f32p, _f32p, _f32p, ctypes.c_uint64, ctypes.c_uint64] + extra + [ctypes.c_double, _f64p]
         L.ph_oracle_saxpy.restype = None
         L.ph_oracle_saxpy.argtypes = [_f32p, _f32p, ctypes.c_float, ctypes.c_uint64, _f32p]
         L.ph_oracle_rel_frobenius.restype = ctypes.c_double
@@ -166,6 +169,22 @@ def flash_rows(q, k, v, scale, rows=None) -> np.ndarray:
                                     _p(rows, _u64p), rows.size, _p(out, _f64p))
     if rc != 0:
         raise MemoryError("oracle flash")
+    return out
+
+
+def kda(q, k, v, g, scale: float, chunk: int | None = None) -> np.ndarray:
+    """Gated linear attention of one head in f64 (examples/kda_fp32.ph): token by token when `chunk` is None
+    (the recurrence the kernel's header states), else chunk by chunk the way the kernel body is written."""
+    q, k, v = (_f32(x) for x in (q, k, v))
+    g = _f32(g).ravel()
+    n, d = q.shape
+    assert k.shape == (n, d) and v.shape == (n, d) and g.size == n
+    out = np.empty((n, d), dtype=np.float64)
+    if chunk is None:
+        lib().ph_oracle_kda_recurrence(_p(q, _f32p), _p(k, _f32p), _p(v, _f32p), _p(g, _f32p), n, d, scale, _p(out, _f64p))
+    else:
+        lib().ph_oracle_kda_chunked(_p(q, _f32p), _p(k, _f32p), _p(v, _f32p), _p(g, _f32p), n, d, chunk, scale,
+                                    _p(out, _f64p))
     return out
 
 

@@ -370,6 +370,76 @@ PH_EXPORT int ph_oracle_flash_rows(uint64_t Nq, uint64_t Nk, uint64_t D, const f
 /* Error measures                                                      */
 /* ------------------------------------------------------------------ */
 /* ||got - want||_F / ||want||_F over n elements (the parity bar). */
+/* Gated linear attention of one head, token by token in f64: the recurrence that
+ * examples/kda_fp32.ph:3-8 states as the meaning of the kernel,
+ *   S_t = a_t * S_{t-1} + k_t^T v_t,   o_t = scale * q_t @ S_t,   a_t = exp(g_t).
+ * The reference has no numeric check for this kernel; this is the definition its chunked
+ * form must agree with.  Q, K, V, O are [n][d] row-major f32, G is [n]. */
+PH_EXPORT void ph_oracle_kda_recurrence(const float *q, const float *k, const float *v, const float *g, uint64_t n, uint64_t d,
+                                       double scale, double *out) {
+  double *S = (double *)calloc(d * d, sizeof(double));
+  for (uint64_t t = 0; t < n; t++) {
+    const double a = exp((double)g[t]);
+    for (uint64_t i = 0; i < d; i++) {
+      const double ki = (double)k[t * d + i];
+      for (uint64_t j = 0; j < d; j++) S[i * d + j] = a * S[i * d + j] + ki * (double)v[t * d + j];
+    }
+    for (uint64_t j = 0; j < d; j++) {
+      double acc = 0.0;
+      for (uint64_t i = 0; i < d; i++) acc += (double)q[t * d + i] * S[i * d + j];
+      out[t * d + j] = scale * acc;
+    }
+  }
+  free(S);
+}
+
+/* The same head computed the way the kernel is written (examples/kda_fp32.ph:27-64): chunks of
+ * `c` tokens, b = cumsum(g), qd = q*exp(b)*scale, kd = k*exp(-b), P = tril(qd kd^T),
+ * o = P v + qd S, S = S*exp(total) + (k*exp(total - b))^T v, in f64. */
+PH_EXPORT void ph_oracle_kda_chunked(const float *q, const float *k, const float *v, const float *g, uint64_t n, uint64_t d,
+                                    uint64_t c, double scale, double *out) {
+  double *S = (double *)calloc(d * d, sizeof(double));
+  double *b = (double *)malloc(c * sizeof(double));
+  double *qd = (double *)malloc(c * d * sizeof(double));
+  double *kd = (double *)malloc(c * d * sizeof(double));
+  double *kf = (double *)malloc(c * d * sizeof(double));
+  double *Sn = (double *)malloc(d * d * sizeof(double));
+  for (uint64_t c0 = 0; c0 < n; c0 += c) {
+    const uint64_t rows = n - c0 < c ? n - c0 : c;
+    double run = 0.0;
+    for (uint64_t r = 0; r < rows; r++) {
+      run += (double)g[c0 + r];
+      b[r] = run;
+    }
+    const double total = run;
+    for (uint64_t r = 0; r < rows; r++)
+      for (uint64_t x = 0; x < d; x++) {
+        qd[r * d + x] = (double)q[(c0 + r) * d + x] * exp(b[r]) * scale;
+        kd[r * d + x] = (double)k[(c0 + r) * d + x] * exp(-b[r]);
+        kf[r * d + x] = (double)k[(c0 + r) * d + x] * exp(total - b[r]);
+      }
+    for (uint64_t i = 0; i < rows; i++)
+      for (uint64_t x = 0; x < d; x++) {
+        double acc = 0.0;
+        for (uint64_t j = 0; j <= i; j++) {
+          double pij = 0.0;
+          for (uint64_t y = 0; y < d; y++) pij += qd[i * d + y] * kd[j * d + y];
+          acc += pij * (double)v[(c0 + j) * d + x];
+        }
+        for (uint64_t y = 0; y < d; y++) acc += qd[i * d + y] * S[y * d + x];
+        out[(c0 + i) * d + x] = acc;
+      }
+    for (uint64_t i = 0; i < d; i++)
+      for (uint64_t x = 0; x < d; x++) {
+        double acc = S[i * d + x] * exp(total);
+        for (uint64_t j = 0; j < rows; j++) acc += kf[j * d + i] * (double)v[(c0 + j) * d + x];
+        Sn[i * d + x] = acc;
+      }
+    memcpy(S, Sn, d * d * sizeof(double));
+  }
+  free(S); free(b); free(qd); free(kd); free(kf); free(Sn);
+}
+
 /* verify_saxpy (phobos-bench/src/main.rs:1179-1188): want[i] = alpha * x[i] + y[i] in f32, a
  * rounded product and then a rounded sum (the volatile keeps the compiler from fusing them). */
 PH_EXPORT void ph_oracle_saxpy(const float *x, const float *y, float alpha, uint64_t n, float *out) {

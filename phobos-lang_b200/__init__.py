@@ -98,6 +98,7 @@ def lib() -> ctypes.CDLL:
             "phobos_device_status": (c.c_int, [vp, c.POINTER(u32)]),
             "phobos_gemm": (c.c_int, [TP, TP, TP, f32, f32, i32, vp, sz, vp]),
             "phobos_saxpy": (c.c_int, [TP, TP, TP, f32, vp]),
+            "phobos_kda": (c.c_int, [TP, TP, TP, TP, TP, f32, vp]),
             "phobos_gemm_workspace_bytes": (sz, [i32, i32, i64, i64, i64]),
             "phobos_gemm_fp16tc_noalloc": (c.c_int, [TP, TP, TP, f32, f32, vp]),
             "phobos_matmul_init": (c.c_int, [TP, f32, i32, vp]),
@@ -250,6 +251,12 @@ def gemm_fp16tc_noalloc(A, B, C, alpha: float, beta: float, stream=None) -> None
     a, b, c = tensor_desc(A), tensor_desc(B), tensor_desc(C)
     check(lib().phobos_gemm_fp16tc_noalloc(ctypes.byref(a), ctypes.byref(b), ctypes.byref(c), alpha, beta,
                                            _stream_ptr(stream)))
+
+
+def kda(Q, K, V, G, O, scale: float, stream=None) -> None:
+    """Chunkwise gated linear attention of one head (examples/kda_fp32.ph): Q, K, V, O [N, 64], G [N, 1]."""
+    d = [tensor_desc(t) for t in (Q, K, V, G, O)]
+    check(lib().phobos_kda(*(ctypes.byref(x) for x in d), scale, _stream_ptr(stream)))
 
 
 def saxpy(x, y, out, alpha: float, stream=None) -> None:

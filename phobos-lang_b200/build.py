@@ -15,7 +15,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 OBJ = HERE / "build"
 LIB = HERE / "libphobos_leaf.so"
-SOURCES = ["api.cu", "gemm_tc.cu", "gemm_tc2.cu", "gemm_f32.cu", "flash.cu", "elementwise.cu", "tmap.cu", "noalloc.cu",
+SOURCES = ["api.cu", "gemm_tc.cu", "gemm_tc2.cu", "gemm_f32.cu", "flash.cu", "elementwise.cu", "kda.cu", "tmap.cu", "noalloc.cu",
            "host.cpp", "executor.cpp", "source.cpp", "planner.cpp", "plan_api.cpp", "wire.cpp"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall", "-Xptxas", "-v"]

@@ -376,6 +376,32 @@ int phobos_saxpy(const PhTensor* x, const PhTensor* y, const PhTensor* out, floa
   return map_launch_rc(rc, "saxpy", err);
 }
 
+int phobos_kda(const PhTensor* Q, const PhTensor* K, const PhTensor* V, const PhTensor* G, const PhTensor* O, float scale,
+               void* stream) {
+  clear_error();
+  View q, k, v, o;
+  int rc;
+  if ((rc = view_of(Q, "Q", &q)) || (rc = view_of(K, "K", &k)) || (rc = view_of(V, "V", &v)) || (rc = view_of(O, "O", &o)))
+    return rc;
+  if (q.dtype != PH_F32 || k.dtype != PH_F32 || v.dtype != PH_F32 || o.dtype != PH_F32)
+    return fail(PH_ERR_UNSUPPORTED, "kda takes f32 tensors");
+  // G is [N, 1]: a column, so the row-length checks of the matrix views do not apply
+  if (!G || !G->ptr) return fail(PH_ERR_INVALID, "G: null tensor");
+  if (G->rank != 2 || G->dtype != PH_F32 || G->sizes[1] != 1 || G->strides[0] < 1 || G->offset < 0)
+    return fail(PH_ERR_INVALID, "G: expected an f32 [N, 1] tensor");
+  const long long N = q.rows, D = q.cols;
+  if (k.rows != N || v.rows != N || o.rows != N || G->sizes[0] != N || k.cols != D || v.cols != D || o.cols != D)
+    return fail(PH_ERR_INVALID, "kda: Q, K, V, O must be [N, D] and G [N, 1] with the same N and D");
+  DeviceState* ds;
+  if ((rc = device_state(&ds))) return rc;
+  const char* err = "";
+  rc = launch_kda(reinterpret_cast<const float*>(q.base), q.ld, reinterpret_cast<const float*>(k.base), k.ld,
+                  reinterpret_cast<const float*>(v.base), v.ld, static_cast<const float*>(G->ptr) + G->offset, G->strides[0],
+                  reinterpret_cast<float*>(o.base), o.ld, static_cast<int>(N), static_cast<int>(D), scale,
+                  static_cast<cudaStream_t>(stream), &err);
+  return map_launch_rc(rc, "kda", err);
+}
+
 // kind_hint: -1, or a PhGemmKind / PH_KIND_AUTO in the low byte, optionally | PH_LAUNCH_STEP_LEAF
 static bool hint_is_step(int32_t kind_hint) { return kind_hint >= 0 && (kind_hint & PH_LAUNCH_STEP_LEAF) != 0; }
 static int gemm_kind_from_types(const PhTensor* t, int32_t kind_hint) {
@@ -459,6 +485,13 @@ int phobos_launch(const char* entry, const PhTensor* t, int32_t n_tensors, const
     float scale;
     if ((rc = scalar_f32(scalars, n_scalars, 4, &scale))) return rc;
     return phobos_flash_attention(&t[0], &t[1], &t[2], &t[3], scale, 1, workspace, workspace_bytes, stream);
+  }
+  if (!strcmp(entry, "kda")) {
+    // kda(Q, K, V, G, O, scale): examples/kda_fp32.ph
+    if (n_tensors != 5) return fail(PH_ERR_INVALID, "kda takes 5 tensors, got %d", n_tensors);
+    float scale;
+    if ((rc = scalar_f32(scalars, n_scalars, 5, &scale))) return rc;
+    return phobos_kda(&t[0], &t[1], &t[2], &t[3], &t[4], scale, stream);
   }
   if (!strcmp(entry, "saxpy")) {
     // saxpy(x, y, out, alpha): examples/saxpy_fp32.ph

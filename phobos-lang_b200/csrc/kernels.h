@@ -47,6 +47,9 @@ int launch_fill_random_block(void* out, int dtype_is_f16, unsigned long long row
                              unsigned long long stream_pitch, float scale, cudaStream_t stream, const char** err);
 int launch_f32_to_f16(const float* in, void* out, unsigned long long n, cudaStream_t stream, const char** err);
 int launch_f16_to_f32(const void* in, float* out, unsigned long long n, cudaStream_t stream, const char** err);
+// Chunkwise gated linear attention of one head (examples/kda_fp32.ph): Q, K, V, O [N, D], G [N, 1]; D = 64
+int launch_kda(const float* Q, long long ldq, const float* K, long long ldk, const float* V, long long ldv, const float* G,
+               long long ldg, float* O, long long ldo, int N, int D, float scale, cudaStream_t stream, const char** err);
 // out = alpha * x + y, one rounded multiply and one rounded add per element
 int launch_saxpy(const float* x, const float* y, float* out, unsigned long long n, float alpha, int sm_count,
                  cudaStream_t stream, const char** err);

@@ -129,3 +129,22 @@ def test_saxpy_rounds_the_product_then_the_sum(oracle):
     for alpha in (2.0, 0.3, -1.7):
         want = (np.float32(alpha) * x) + y              # numpy rounds each f32 operation
         assert np.array_equal(oracle.saxpy(x, y, alpha).view(np.uint32), want.view(np.uint32))
+
+
+def test_kda_chunked_form_equals_the_recurrence(oracle):
+    """The chunked evaluation the kernel body spells out (cumsum / tril / carried state) is the token-by-token
+    recurrence S_t = a_t S_{t-1} + k_t^T v_t, o_t = scale q_t S_t of its header (examples/kda_fp32.ph:3-18),
+    for any chunk size, ragged tails included."""
+    n, d = 200, 64
+    q, k, v = (oracle.lcg_fill(s, n * d).reshape(n, d) for s in (7, 8, 9))
+    g = -np.abs(oracle.lcg_fill(10, n)) * 0.2            # log forget-gates, <= 0
+    want = oracle.kda(q, k, v, g, 0.125)
+    assert np.abs(want).max() > 0.1
+    for chunk in (1, 32, 64, 128, 200):
+        got = oracle.kda(q, k, v, g, 0.125, chunk=chunk)
+        assert np.abs(got - want).max() <= 1e-12 * max(1.0, np.abs(want).max())
+    # a known answer: gates of zero (a_t = 1) and orthonormal keys make S a plain sum of outer products
+    e = np.eye(4, 64, dtype=np.float32)
+    vv = np.arange(4 * 64, dtype=np.float32).reshape(4, 64)
+    out = oracle.kda(e, e, vv, np.zeros(4, np.float32), 1.0)
+    assert np.array_equal(out, vv.astype(np.float64))     # o_t = q_t S_t = v_t
