@@ -39,10 +39,10 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # captures summarised under profiles/; None where no capture exists yet.
 NCU_TRAFFIC_BYTES = {
     "gemm_fp16tc_fp32acc": 152_248_320 + 40_332_544,       # profiles/gemm_tc2_fp16tc_fp32acc_4096.md
-    "gemm_fp32": 423_293_184 + 55_824_896,                 # profiles/gemm_f32_4096_and_16384.md
+    "gemm_fp32": 424_483_840 + 53_399_808,                 # profiles/gemm_f32_4096_and_16384.md
     "gemm_fp16": 1_189_407_000 + 124_635_648,              # profiles/gemm_tc2_fp16_8192.md
     "flash_fp16": 402_703_360 + 110_934_528,               # profiles/flash_fwd_fp16_bh128_s4096_d128.md
-    "matmul_cluster_fp32": 56_757_379_328 + 1_097_407_232,  # 16384^3 on one GPU, same file as gemm_fp32
+    "matmul_cluster_fp32": 27_178_051_328 + 1_085_768_960,  # 16384^3 on one GPU, same file as gemm_fp32
     "saxpy_fp32": 268_465_664 + 90_302_720,                 # profiles/saxpy_fp32_n2p25.md
 }
 
