@@ -106,7 +106,7 @@ def test_executor_reports_arena_exhaustion_and_bad_programs(ph, dev):
             ex.run()
         assert e.value.code == ph.PH_ERR_STATE and "arena exhausted" in e.value.message   # engine.rs:752-775
     with ph.Executor(0, 0, 1 << 20) as ex:
-        ex.set_kernel(0, "kda")       # a reference kernel with no native leaf here
+        ex.set_kernel(0, "conv2d")    # no such leaf
         ex.issue([I(iid=1, op=ph.OP_ALLOC, tile=tid(0, 0, 0), shape=(64, 64), data_type=ph.F32),
                   I(iid=2, op=ph.OP_COMPUTE, kernel=0, args=((tid(0, 0, 0), ph.RMW),), deps=(1,))])
         with pytest.raises(ph.PhobosError) as e:

@@ -195,7 +195,7 @@ def test_rejects_bad_descriptors(ph, dev):
         ph.gemm(A, torch.zeros(32, 64, device=dev), A, 1.0, 0.0, ph.GEMM_FP32)   # K mismatch
     assert e.value.code == ph.PH_ERR_INVALID
     with pytest.raises(ph.PhobosError) as e:
-        ph.launch("kda", [A], [])
+        ph.launch("conv2d", [A], [])
     assert e.value.code == ph.PH_ERR_UNSUPPORTED
 
 
