@@ -57,6 +57,9 @@ struct Tc2Params {
   int split_first;      // index of the first split tile
   uint32_t* flags;      // hand-over words between the K ranges of a tile
   uint32_t epoch;       // distinguishes this launch's hand-overs from older ones
+  // split-N of the last, partly filled round: its tiles are cut into two column halves (bn / 2 wide), so
+  // that twice as many CTA pairs finish the launch together.  Unlike split-K the halves are independent.
+  int nsplit;           // 1 = off, 2 = on (needs bn == 256; never together with split > 1)
   // 2: two tiles of a pair are in flight at once, each with its own producer, issuer,
   // accumulator buffer and half of the stage ring (see the kernel comment); 1: one tile
   int streams;
@@ -66,14 +69,26 @@ struct Tc2Params {
 // tiles; after them come `split` consecutive units per remaining tile.
 struct Unit {
   int tile, part, kb0, kb1;
+  int bn;        // width of this unit's output tile
+  int col_off;   // its first column inside the tile's bn-wide column block
 };
 __device__ __forceinline__ Unit unit_of(int u, const Tc2Params& p, int num_kb) {
   Unit w;
+  w.bn = p.bn;
+  w.col_off = 0;
   if (u < p.split_first) {
     w.tile = u;
     w.part = 0;
     w.kb0 = 0;
     w.kb1 = num_kb;
+  } else if (p.nsplit > 1) {
+    const int v = u - p.split_first;
+    w.tile = p.split_first + v / p.nsplit;
+    w.part = v % p.nsplit;
+    w.kb0 = 0;
+    w.kb1 = num_kb;
+    w.bn = p.bn / p.nsplit;
+    w.col_off = w.part * w.bn;
   } else {
     const int v = u - p.split_first;
     w.tile = p.split_first + v / p.split;
@@ -151,11 +166,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
   const int num_tiles = p.tiles_m * p.tiles_n;
   const int num_kb = (p.K + BK - 1) / BK;
-  const int num_units = p.split_first + (num_tiles - p.split_first) * p.split;
+  const int num_units = p.split_first + (num_tiles - p.split_first) * (p.nsplit > 1 ? p.nsplit : p.split);
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
-  const int half_n = p.bn >> 1;                 // B columns staged by each CTA
-  const int nbox = (half_n + 63) >> 6;
 
   // Stream s (0 or 1) works on the pair's units n = s, s + streams, ... (unit n of a
   // pair is launch unit pair + n * num_pairs), accumulates into buffer n & 1 and owns
@@ -169,7 +182,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      const uint32_t stage_tx = 2u * static_cast<uint32_t>(A_BYTES + nbox * (BK * 128));
       for (int n = sidx; ok; n += p.streams) {
         const int u = pair + n * num_pairs;
         if (u >= num_units) break;
@@ -177,7 +189,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         int mb, nb;
         pair_tile_coords(w.tile, p, mb, nb);
         const int row0 = mb * (2 * BM) + static_cast<int>(rank) * BM;
-        const int col0 = nb * p.bn + static_cast<int>(rank) * half_n;
+        const int half_n = w.bn >> 1;                 // B columns staged by each CTA
+        const int nbox = (half_n + 63) >> 6;
+        const uint32_t stage_tx = 2u * static_cast<uint32_t>(A_BYTES + nbox * (BK * 128));
+        const int col0 = nb * p.bn + w.col_off + static_cast<int>(rank) * half_n;
         for (int kb = w.kb0; kb < w.kb1; kb++) {
           const int st = s0 + stage;
           if (!mbar_wait(&empty[st], phase ^ 1, SITE_GEMM_PRODUCER_EMPTY, wctx)) {
@@ -200,7 +215,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     // ------------------------------ MMA issuers (leader CTA) ---------------------
     const int sidx = warp >> 1;
     if (leader && lane == 0 && sidx < p.streams) {
-      const uint32_t idesc = umma_idesc_f16(2 * BM, p.bn, !ACC_F16, /*a_mn=*/false, /*b_mn=*/true);
       const int s0 = sidx * ring;
       int stage = 0;
       uint32_t phase = 0;
@@ -209,6 +223,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const int u = pair + n * num_pairs;
         if (u >= num_units) break;
         const Unit w = unit_of(u, p, num_kb);
+        const uint32_t idesc = umma_idesc_f16(2 * BM, w.bn, !ACC_F16, /*a_mn=*/false, /*b_mn=*/true);
         const int acc = n & 1;
         const uint32_t acc_phase = (n >> 1) & 1;
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, SITE_GEMM_MMA_TMEM_EMPTY, wctx)) break;
@@ -253,7 +268,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       // for the hand-over word of this warp's 32 rows (same CTA rank, same warp)
       float beta = p.beta;
       uint32_t* flag = nullptr;
-      if (u >= p.split_first) {
+      if (p.split > 1 && u >= p.split_first) {
         flag = p.flags + ((((p.epoch % FLAG_BANKS) * FLAG_TILES + (w.tile - p.split_first)) * 2 + rank) * 4 + q);
         if (w.part > 0) {
           beta = 1.0f;
@@ -278,8 +293,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       const bool row_ok = row < p.M;
       CT* crow = reinterpret_cast<CT*>(p.C) + static_cast<long long>(row) * p.ldc;
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * ACC_STRIDE;
-      const int col_end = min(p.N, (nb + 1) * p.bn);
-      const int chunks = (p.bn + 31) >> 5;
+      const int tile_col0 = nb * p.bn + w.col_off;
+      const int col_end = min(p.N, tile_col0 + w.bn);
+      const int chunks = (w.bn + 31) >> 5;
       if constexpr (sizeof(CT) == 4) {
         // f32 C.  The accumulator arrives one row per lane; going to global memory that
         // way makes every warp instruction touch 32 different rows (16 useful bytes per
@@ -292,7 +308,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const long long row_base = static_cast<long long>(mb) * (2 * BM) + static_cast<int>(rank) * BM + q * 32;
 #pragma unroll 1
         for (int c = 0; c < chunks; c++) {
-          const int col = nb * p.bn + c * 32 + sub_col;
+          const int col = tile_col0 + c * 32 + sub_col;
           const bool col_ok = col < col_end;
           float4 old[8];
 #pragma unroll
@@ -329,7 +345,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         uint32_t r[32];
         tmem_ld_32x32b_x32(t_addr + c * 32, r);
         tmem_ld_wait();
-        const int col0 = nb * p.bn + c * 32;
+        const int col0 = tile_col0 + c * 32;
         if (row_ok && col0 < col_end) {
           {
 #pragma unroll
@@ -405,7 +421,7 @@ cudaError_t launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const Tc
   if (e != cudaSuccess) return e;
   const int tiles = p.tiles_m * p.tiles_n;
   const int pairs = sm_count / 2;
-  const int units = p.split_first + (tiles - p.split_first) * p.split;
+  const int units = p.split_first + (tiles - p.split_first) * (p.nsplit > 1 ? p.nsplit : p.split);
   const int grid = 2 * (units < pairs ? units : pairs);
   kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, p);
   return cudaGetLastError();
@@ -474,6 +490,18 @@ int launch_gemm_tc_pair(const void* A, long long lda, const void* B, long long l
         p.flags = g_split_flags_addr[dev];
         p.epoch = __atomic_add_fetch(&g_epoch, 1u, __ATOMIC_RELAXED);
       }
+    }
+  }
+  // split-N tail: with 256-wide tiles and a last round that fills at most half of the pairs, the last
+  // round's tiles are computed as 128-wide halves (a 128-wide pair MMA takes ~122 clocks against ~171
+  // for 256, so the round shrinks from 43.8 K to 31.2 K clocks at K = 4096).  PHOBOS_GEMM_NSPLIT=0 turns it off.
+  p.nsplit = 1;
+  {
+    const char* ns = getenv("PHOBOS_GEMM_NSPLIT");
+    const bool want = !(ns && ns[0] == '0');
+    if (want && p.split == 1 && p.bn == 256 && tiles > pairs && rem > 0 && 2 * rem <= pairs && N % 256 == 0) {
+      p.nsplit = 2;
+      p.split_first = tiles - rem;
     }
   }
   // PHOBOS_GEMM_STREAMS=2 keeps two tiles of a pair in flight, each with its own producer,

@@ -268,3 +268,23 @@ def test_saxpy_bit_exact(ph, oracle, dev, n):
         assert not np.array_equal(fused, want)
     with pytest.raises(ph.PhobosError):
         ph.saxpy(X, Y[: n - 4] if n > 4 else Y.reshape(2, 2), O, 1.0)
+
+
+@pytest.mark.parametrize("nsplit", ["1", "0"])
+def test_gemm_fp16tc_split_n_tail(ph, oracle, dev, monkeypatch, nsplit):
+    """The last, partly filled round of 256-wide tiles computed as 128-wide halves (default) or not."""
+    monkeypatch.setenv("PHOBOS_GEMM_NSPLIT", nsplit)
+    M, N, K = 4864, 1024, 512           # 76 pair tiles on 74 pairs: 2 tiles left over -> 4 half tiles
+    a, b, c = _inputs(oracle, M, N, K)
+    a16, b16 = oracle.fp16_round(a), oracle.fp16_round(b)
+    rows = np.unique(np.concatenate([np.arange(0, M, 89, dtype=np.uint64), np.arange(M - 512, M, 3, dtype=np.uint64)]))
+    want = oracle.gemm_rows(a16, b16, c, 0.5, 1.5, rows=rows)
+    A, B, C = _to(dev, a16, True), _to(dev, b16, True), _to(dev, c)
+    ph.gemm(A, B, C, 0.5, 1.5, ph.GEMM_FP16TC_FP32ACC)
+    assert ph.device_status() == 0
+    assert oracle.rel_frobenius(C.cpu().numpy()[rows.astype(int)], want) <= TOL_F16TC
+    # the f16-accumulate kernel shares the scheduler
+    Ch = _to(dev, oracle.fp16_round(c), True)
+    ph.gemm(A, B, Ch, 1.0, 1.0, ph.GEMM_FP16)
+    want16 = oracle.gemm_rows(a16, b16, oracle.fp16_round(c), 1.0, 1.0, rows=rows)
+    assert oracle.rel_frobenius(Ch.float().cpu().numpy()[rows.astype(int)], want16) <= TOL_F16
