@@ -341,6 +341,15 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t cta_mas
       : "memory");
 }
 
+// Programmatic dependent launch.  A kernel launched with launch_with_pdl() may start while the
+// kernel before it on the stream is still draining: pdl_launch_dependents() lets the next kernel's
+// CTAs be scheduled as soon as this grid is resident, pdl_wait() blocks until every earlier kernel
+// has completed and its writes are visible.  Everything before pdl_wait() must touch no global
+// memory another kernel may write (barrier setup, tensor-memory allocation, descriptor prefetch).
+// Both are no-ops in a kernel that was launched the ordinary way.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // Named barrier among a subset of warps (id 1..15; 0 is __syncthreads).
 __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");

@@ -10,6 +10,7 @@
 // steps sequentially, so the values are those of the sequential generator.
 #include <cuda_fp16.h>
 
+#include "common.cuh"
 #include "kernels.h"
 
 namespace ph {
@@ -160,6 +161,8 @@ __global__ void __launch_bounds__(BLOCK) saxpy_once_kernel(const float4* __restr
                                                            float4* __restrict__ out, unsigned long long n4, float alpha,
                                                            const float* x_tail, const float* y_tail, float* out_tail, int tail) {
   const unsigned long long base = static_cast<unsigned long long>(blockIdx.x) * (BLOCK * UNR) + threadIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
   float4 a[UNR], b[UNR];
 #pragma unroll
   for (int u = 0; u < UNR; u++) {
@@ -271,10 +274,15 @@ int launch_saxpy(const float* x, const float* y, float* out, unsigned long long 
   constexpr int BLOCK = 256, UNR = 4;
   (void)sm_count;
   const unsigned long long blocks = (n4 + BLOCK * UNR - 1) / (BLOCK * UNR);
-  saxpy_once_kernel<BLOCK, UNR><<<static_cast<unsigned>(blocks < 1 ? 1 : blocks), BLOCK, 0, stream>>>(
-      reinterpret_cast<const float4*>(x), reinterpret_cast<const float4*>(y), reinterpret_cast<float4*>(out), n4, alpha,
-      x + n4 * 4, y + n4 * 4, out + n4 * 4, tail);
-  return check(err);
+  cudaError_t e = launch_with_pdl(saxpy_once_kernel<BLOCK, UNR>, dim3(static_cast<unsigned>(blocks < 1 ? 1 : blocks)),
+                                  dim3(BLOCK), 0, stream, reinterpret_cast<const float4*>(x),
+                                  reinterpret_cast<const float4*>(y), reinterpret_cast<float4*>(out), n4, alpha,
+                                  static_cast<const float*>(x + n4 * 4), static_cast<const float*>(y + n4 * 4), out + n4 * 4, tail);
+  if (e != cudaSuccess) {
+    *err = cudaGetErrorString(e);
+    return -3;
+  }
+  return 0;
 }
 
 }  // namespace ph

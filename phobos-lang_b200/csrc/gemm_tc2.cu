@@ -163,6 +163,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   cluster_sync_all();  // the peer's barriers exist before anything signals them
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+  pdl_wait();   // nothing above reads or writes global memory; everything below may
 
   const int num_tiles = p.tiles_m * p.tiles_n;
   const int num_kb = (p.K + BK - 1) / BK;
@@ -423,8 +425,7 @@ cudaError_t launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const Tc
   const int pairs = sm_count / 2;
   const int units = p.split_first + (tiles - p.split_first) * (p.nsplit > 1 ? p.nsplit : p.split);
   const int grid = 2 * (units < pairs ? units : pairs);
-  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, p);
-  return cudaGetLastError();
+  return launch_with_pdl(kern, dim3(grid), dim3(NUM_THREADS), SMEM_BYTES, stream, tmA, tmB, p);
 }
 
 }  // namespace

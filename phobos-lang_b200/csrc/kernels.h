@@ -1,9 +1,33 @@
 // Internal launcher interface between api.cu and the kernel translation units.
 #pragma once
+#include <cstdlib>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
 namespace ph {
+
+// Launches `kernel` so that its prologue may overlap the tail of the kernel before it on the stream
+// (programmatic stream serialization); the kernel calls pdl_wait() before its first dependent access.
+// PHOBOS_PDL=0 falls back to an ordinary launch.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_with_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  static const bool off = [] {
+    const char* e = getenv("PHOBOS_PDL");
+    return e && e[0] == '0';
+  }();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = off ? 0 : 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 
 // gemm_tc.cu — f16 operands on tcgen05 tensor cores.
 int launch_gemm_tc(const void* A, long long lda, const void* B, long long ldb, void* C, long long ldc, int M, int N,
