@@ -433,8 +433,17 @@ def bench_partitioned(ctx: Ctx, world: int, rank: int, MNK: int, alpha: float, b
     # selects the broadcast form instead
     peers, exchange = None, "nccl"
     if os.environ.get("PHOBOS_EXCHANGE", "p2p") == "p2p":
-        peers = part.PeerShards(plan, rank, a_shard, b_shard)
-        exchange = "p2p"
+        # every rank must take the same path: agree on whether symmetric memory came up everywhere
+        try:
+            peers = part.PeerShards(plan, rank, a_shard, b_shard)
+            ok = torch.ones(1, device=dev)
+        except Exception as ex:  # noqa: BLE001 - reported, then the collective form is used
+            print(f"rank {rank}: symmetric memory unavailable ({ex}); using NCCL broadcasts", file=sys.stderr)
+            peers, ok = None, torch.zeros(1, device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if float(ok.item()) == 0.0:
+            peers = None
+        exchange = "p2p" if peers is not None else "nccl"
     pa, pb = (peers.a, peers.b) if peers is not None else (a_shard, b_shard)
 
     def step(i):
