@@ -10,9 +10,13 @@ N = 1: the headline workload is gemm_fp16tc_fp32acc at M=N=K=4096 (f16 A/B, f32
 accumulate and C, alpha 1, beta 0); the other single-GPU configurations
 (gemm_fp32 4096^3, gemm_fp16 8192^3, flash_fp16 B4 H32 S4096 D128,
 matmul_cluster_fp32 16384^3 on one GPU) are measured the same way and reported
-under "suite".  N > 1: the partitioned matmul_cluster_fp32 16384^3 (2-D C
-partition, A/B panels exchanged over NVLink), strong scaling, launched one rank
-per GPU under torchrun.
+under "suite".  N > 1 (one rank per GPU under torchrun): `value` is the same
+headline workload as N independent replicas, one per GPU, timed between barriers
+with the maximum over the ranks (weak scaling; the single-GPU leaves do not shard),
+so the values at N = 1, 2, 4, 8 form one series.  The one configuration that IS
+partitioned across GPUs, matmul_cluster_fp32 16384^3 (2-D C partition, A/B panels
+copied over NVLink), is measured in the same run and reported under "partitioned"
+(strong scaling; its single-GPU point is suite.matmul_cluster_fp32 of the N = 1 line).
 
 `--impl reference` times the reference's CPU arithmetic for the same workload (the
 oracle port of its f64 verifier math, all host threads) on a bounded sample.
@@ -140,6 +144,7 @@ class Ctx:
         self.ph, self.torch, self.dev, self.steps, self.warmup = ph, torch, dev, steps, warmup
         self.windows = []
         self.cpu_seconds = 1.0   # length of the CPU-baseline sample of the next workload
+        self.barrier = None      # N > 1: every timed region starts and ends at a barrier across the ranks
 
     def time_steps(self, fn_step, steps=None, warmup=None, barrier=None, finish=None):
         """Runs warm-up steps, then times `steps` steps: total by one event pair around
@@ -147,6 +152,7 @@ class Ctx:
         torch = self.torch
         steps = self.steps if steps is None else steps
         warmup = self.warmup if warmup is None else warmup
+        barrier = barrier or self.barrier
         for i in range(warmup):
             fn_step(i)
         if finish:
@@ -607,22 +613,42 @@ def main():
             raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})")
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
+        # (1) the headline workload as N independent replicas, one per GPU: no exchange, weak scaling
+        ctx.barrier = dist.barrier
+        head = bench_gemm(ctx, "gemm_fp16tc_fp32acc", 4096, 4096, 4096, 1.0, 0.0, peaks, cpu_baseline=False)
+        t = torch.tensor([head["ms_per_step"], head["e2e"]["ms_per_step"]], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_head, ms_head_e2e = (float(x) for x in t.tolist())
+        fl = gemm_flops(4096, 4096, 4096)
+        # (2) the one configuration that is partitioned across GPUs: matmul_cluster_fp32 16384^3, strong scaling
+        ctx.barrier = None
         res = bench_partitioned(ctx, world, rank, 16384, 0.125, 1.5)
         if rank == 0:
-            res["cpu_baseline"] = None
-            line = {"metric": metric, "value": res["tflops"], "unit": "TFLOP/s", "n_gpus": world,
-                    "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["ms_per_step"],
-                    "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            line = {"metric": metric, "value": world * fl / (ms_head * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
+                    "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_head,
+                    "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 x f16 -> f32",
                     "data": "synthetic (seeded Lcg streams of phobos-base/src/rng.rs, generated on the device)",
-                    "config": {"workload": "matmul_cluster_fp32", "M": 16384, "N": 16384, "K": 16384, "alpha": 0.125,
-                               "beta": 1.5, "parallelism": f"2-D C partition {res['grid']}, K chunks of {res['k_chunk']}"
-                               " copied over NVLink one step ahead of the step leaf ("
-                               + ("peer copies out of the home ranks' shards, no collective" if res["exchange"] == "p2p"
-                                  else "NCCL broadcast") + ")",
-                               "l2": "operands (1 GiB each) exceed L2"},
-                    "roofline": res["roofline"], "e2e": {k: v for k, v in res["e2e"].items()},
-                    "gpu_launches": res["gpu_launches"], "peer_bytes_per_step": res["peer_bytes_per_step"],
-                    "direct_load_bound": res["direct_load_bound"]}
+                    "config": {"workload": "gemm_fp16tc_fp32acc", "M": 4096, "N": 4096, "K": 4096, "alpha": 1.0, "beta": 0.0,
+                               "parallelism": f"{world} independent replicas, one per GPU (the single-GPU leaves do not "
+                               "shard: replicas only); the partitioned configuration is under \"partitioned\"",
+                               "l2": f"{head.get('input_sets', 1)} rotating input sets, working set larger than L2"},
+                    "roofline": head["roofline"], "cpu_baseline": None,
+                    "e2e": {"value": world * fl / (ms_head_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_head_e2e,
+                            "h2d_bytes_per_step": world * head["e2e"]["h2d_bytes_per_step"],
+                            "d2h_bytes_per_step": world * head["e2e"]["d2h_bytes_per_step"]},
+                    "gpu_launches": args.steps * world,
+                    "partitioned": {
+                        "workload": "matmul_cluster_fp32", "M": 16384, "N": 16384, "K": 16384, "alpha": 0.125, "beta": 1.5,
+                        "scaling": "strong", "value": res["tflops"], "unit": "TFLOP/s", "ms_per_step": res["ms_per_step"],
+                        "dtype": "f32",
+                        "parallelism": f"2-D C partition {res['grid']}, K chunks of {res['k_chunk']}"
+                        " copied over NVLink one step ahead of the step leaf ("
+                        + ("peer copies out of the home ranks' shards, no collective" if res["exchange"] == "p2p"
+                           else "NCCL broadcast") + ")",
+                        "roofline": res["roofline"], "e2e": {k: v for k, v in res["e2e"].items()},
+                        "gpu_launches": res["gpu_launches"], "peer_bytes_per_step": res["peer_bytes_per_step"],
+                        "direct_load_bound": res["direct_load_bound"],
+                        "single_gpu_value_is_in": "suite.matmul_cluster_fp32 of the --gpus 1 line"}}
         dist.barrier()
         sampler.stop()
         if rank == 0:
