@@ -261,41 +261,51 @@ def bench_gemm(ctx: Ctx, name: str, M: int, N: int, K: int, alpha: float, beta: 
     return out
 
 
-def bench_flash(ctx: Ctx, BH: int, S: int, D: int, peaks, cpu_baseline=True, e2e=True):
+def bench_flash(ctx: Ctx, BH: int, S: int, D: int, peaks, cpu_baseline=True, e2e=True, f32_storage=False):
+    """flash_fp16, or with f32_storage flash_fp32: f32 Q/K/V/O, staged to f16 by a convert pass inside the
+    timed step, the same tensor-core kernel, O written as f32 by its epilogue."""
     ph, torch, dev = ctx.ph, ctx.torch, ctx.dev
     scale = 1.0 / math.sqrt(D)
-    Q, K, V = (torch.empty((BH, S, D), dtype=torch.float16, device=dev) for _ in range(3))
+    dt = torch.float32 if f32_storage else torch.float16
+    Q, K, V = (torch.empty((BH, S, D), dtype=dt, device=dev) for _ in range(3))
     for t, seed in ((Q, 4), (K, 5), (V, 6)):
         ph.fill_random(t, seed=seed, normal=True)   # N(0,1): Box-Muller over the Lcg stream (no reference analogue)
     O = torch.empty_like(Q)
+    ws = None
+    if f32_storage:
+        ws = torch.empty((ph.flash_workspace_bytes(ph.F32, BH, S, S, D),), dtype=torch.uint8, device=dev)
 
     def step(i):
-        ph.flash_attention(Q, K, V, O, scale)
+        ph.flash_attention(Q, K, V, O, scale, workspace=ws)
 
     ms_total, ms_launch, ms_min = ctx.time_steps(step)
     ph.device_status()
     flops = 4.0 * BH * S * S * D
     ach = flops / (ms_launch * 1e-3) / 1e12
     peak = peaks["bf16_tflops"]
-    out = {"workload": "flash_fp16", "batch_heads": BH, "seq_len": S, "head_dim": D,
+    out = {"workload": "flash_fp32" if f32_storage else "flash_fp16", "batch_heads": BH, "seq_len": S, "head_dim": D,
            "tflops": flops / (ms_total * 1e-3) / 1e12, "ms_per_step": ms_total, "ms_per_launch": ms_launch,
            "ms_min": ms_min, "exp_per_s": BH * S * S / (ms_launch * 1e-3),
            "roofline": {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
                         "peak_source": f"of {peaks['_source']} (burst cuBLAS bf16)",
-                        "frac_of_nominal_2250": ach / NOMINAL_F16_TFLOPS, "traffic": NCU_TRAFFIC_BYTES.get("flash_fp16")}}
+                        "frac_of_nominal_2250": ach / NOMINAL_F16_TFLOPS,
+                        "traffic": None if f32_storage else NCU_TRAFFIC_BYTES.get("flash_fp16")}}
+    if f32_storage:
+        out["launches_per_step"] = 4      # three f32 -> f16 staging passes and the attention kernel
     if e2e:
         hQ, hK, hV = (pinned_like(torch, t) for t in (Q, K, V))
         hO = torch.empty(O.shape, dtype=O.dtype, device="cpu", pin_memory=True)
 
         pipe = ph.HostPipeline(torch, dev, [(t.shape, t.dtype) for t in (Q, K, V, O)],
-                               lambda q, k, v, o, stream: ph.flash_attention(q, k, v, o, scale, stream=stream), result_index=3)
+                               lambda q, k, v, o, stream: ph.flash_attention(q, k, v, o, scale, workspace=ws, stream=stream),
+                               result_index=3)
 
         def e2e_step(i):
             pipe.submit((hQ, hK, hV, None), hO)
 
         ms_e2e, _, _ = ctx.time_steps(e2e_step, steps=max(6, min(ctx.steps, 20)), warmup=3, finish=pipe.join)
         del pipe
-        nb = Q.numel() * 2
+        nb = Q.numel() * Q.element_size()
         out["e2e"] = {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
                       "h2d_bytes_per_step": 3 * nb, "d2h_bytes_per_step": nb}
     if cpu_baseline:
@@ -580,7 +590,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-suite", action="store_true", help="headline workload only")
-    ap.add_argument("--only", default=None, help="run one suite workload as the headline (profiling)")
+    ap.add_argument("--only", "--bench", dest="only", default=None,
+                    help="run one workload as the headline (the reference bench's --bench NAME)")
+    ap.add_argument("--csv", nargs="?", const="results.csv", default=None,
+                    help="also write the reference bench's CSV (phobos-bench/src/report.rs:71-88) to PATH")
+    ap.add_argument("--peak-fp32", type=float, default=None, help="TFLOP/s; overrides the fp32 peak of the CSV")
+    ap.add_argument("--peak-fp16tc", type=float, default=None, help="TFLOP/s; overrides the f16-tc peak of the CSV")
+    ap.add_argument("--peak-fp16tcf32acc", type=float, default=None,
+                    help="TFLOP/s; overrides the f16-tc-f32-acc peak of the CSV")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -663,6 +680,7 @@ def main():
         "gemm_fp32": lambda: bench_gemm(ctx, "gemm_fp32", 4096, 4096, 4096, 0.125, 1.5, peaks, cpu),
         "gemm_fp16": lambda: bench_gemm(ctx, "gemm_fp16", 8192, 8192, 8192, 1.0, 1.0, peaks, cpu),
         "flash_fp16": lambda: bench_flash(ctx, 128, 4096, 128, peaks, cpu),
+        "flash_fp32": lambda: bench_flash(ctx, 128, 4096, 128, peaks, cpu_baseline=False, f32_storage=True),
         "matmul_cluster_fp32": lambda: bench_gemm(ctx, "matmul_cluster_fp32", 16384, 16384, 16384, 0.125, 1.5, peaks,
                                                   cpu_baseline=False, e2e=False),
         "saxpy_fp32": lambda: bench_saxpy(ctx, 1 << 25, peaks, cpu),
@@ -689,7 +707,31 @@ def main():
                        "l2": f"{head.get('input_sets', 1)} rotating input sets, working set larger than L2"},
             "roofline": head["roofline"], "cpu_baseline": head.get("cpu_baseline"), "e2e": head.get("e2e"),
             "gpu_launches": args.steps, "clocks": sampler.summary(ctx.windows), "suite": suite}
+    if args.csv:
+        write_csv(args.csv, {head_name: head, **suite}, args, ph.device_info(dev.index or 0))
     print(json.dumps(line), flush=True)
+
+
+def write_csv(path, results, args, info):
+    """The reference bench's CSV (columns and precision labels of phobos-bench/src/report.rs:18-25, 71-88), then
+    this build's extra columns.  Peaks: fp32 from the device (SMs x 128 lanes x 2 x clock, report.rs:125-147);
+    both tensor-core precisions at the part's dense f16 rate (B200 accumulates in f32 at full rate, unlike the
+    consumer parts the reference halves); the --peak-* flags override, as in the reference."""
+    peaks = {"f32": (args.peak_fp32 * 1e3) if args.peak_fp32 else info.fp32_peak_flops / 1e9,
+             "f16-tc": (args.peak_fp16tc or NOMINAL_F16_TFLOPS) * 1e3,
+             "f16-tc-f32-acc": (args.peak_fp16tcf32acc or NOMINAL_F16_TFLOPS) * 1e3}
+    precision = {"gemm_fp32": "f32", "matmul_cluster_fp32": "f32", "saxpy_fp32": "f32", "gemm_fp16": "f16-tc",
+                 "gemm_fp16tc_fp32acc": "f16-tc-f32-acc", "flash_fp16": "f16-tc-f32-acc", "flash_fp32": "f16-tc-f32-acc"}
+    rows = ["benchmark,impl,precision,gflops,peak_gflops,pct_of_peak,n_gpus,ms_per_launch,roofline_bound,roofline_frac"]
+    for name, r in results.items():
+        prec = precision[name]
+        gf = r["tflops"] * 1e3
+        rows.append(f"{name},phobos-b200,{prec},{gf:.1f},{peaks[prec]:.1f},{100.0 * gf / peaks[prec]:.1f},1,"
+                    f"{r['ms_per_launch']:.4f},{r['roofline']['bound']},{r['roofline']['frac']:.3f}")
+        cb = r.get("cpu_baseline")
+        if cb:
+            rows.append(f"{name},cpu-{cb['kind']},f64,{cb['value'] * 1e3:.1f},,,0,,,")
+    Path(path).write_text("\n".join(rows) + "\n")
 
 
 if __name__ == "__main__":
