@@ -68,6 +68,8 @@ def lib() -> ctypes.CDLL:
         L.ph_oracle_max_rel_floor.restype = ctypes.c_double
         L.ph_oracle_max_rel_floor.argtypes = [_f32p, _f64p, ctypes.c_uint64, ctypes.c_double]
         L.ph_oracle_threads.restype = ctypes.c_int
+        L.ph_oracle_set_threads.restype = None
+        L.ph_oracle_set_threads.argtypes = [ctypes.c_int]
         _lib = L
     return _lib
 
@@ -82,6 +84,15 @@ def _f32(a) -> np.ndarray:
 
 def threads() -> int:
     return int(lib().ph_oracle_threads())
+
+
+def use_all_cores() -> int:
+    """Sets the OpenMP thread count to the cores this process may run on (a launcher such as torchrun
+    exports OMP_NUM_THREADS=1 to its workers) and returns it."""
+    import os
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().ph_oracle_set_threads(n)
+    return threads()
 
 
 def lcg_u64(seed: int, n: int) -> list[int]:

@@ -481,3 +481,13 @@ PH_EXPORT int ph_oracle_threads(void) {
   return 1;
 #endif
 }
+
+/* Number of threads of the following parallel regions (a launcher may have exported
+ * OMP_NUM_THREADS=1 for its worker processes). */
+PH_EXPORT void ph_oracle_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
