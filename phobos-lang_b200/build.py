@@ -70,7 +70,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
 
 def build_probes() -> Path:
-    """Compiles the diagnostic pipe-rate probe (csrc/probes/pipe_probe.cu) into phobos-lang_b200/pipe_probe."""
+    """Compiles the diagnostics: the pipe-rate probe (csrc/probes/pipe_probe.cu -> phobos-lang_b200/pipe_probe)
+    and the SM clock sampler (csrc/probes/clock_spy.cu -> phobos-lang_b200/libclock_spy.so)."""
     out = HERE / "pipe_probe"
     env = dict(os.environ)
     env.pop("CC", None)
@@ -80,6 +81,12 @@ def build_probes() -> Path:
     r = subprocess.run(cmd, capture_output=True, text=True, env=env)
     if r.returncode != 0:
         raise RuntimeError(f"nvcc failed for pipe_probe.cu:\n{r.stdout}\n{r.stderr}")
+    spy = HERE / "libclock_spy.so"
+    cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-shared", "-Xcompiler", "-fPIC",
+           "-o", str(spy), str(CSRC / "probes" / "clock_spy.cu")]
+    r = subprocess.run(cmd, capture_output=True, text=True, env=env)
+    if r.returncode != 0:
+        raise RuntimeError(f"nvcc failed for clock_spy.cu:\n{r.stdout}\n{r.stderr}")
     return out
 
 
