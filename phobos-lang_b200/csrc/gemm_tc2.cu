@@ -459,6 +459,10 @@ int launch_gemm_tc_pair(const void* A, long long lda, const void* B, long long l
   // a raster band keeps about 32 MB of A rows hot in L2 while the B panels stream past
   long long g = (32ll << 20) / (2ll * BM * static_cast<long long>(K) * 2);
   p.group_m = static_cast<int>(g < 1 ? 1 : (g > 16 ? 16 : g));
+  if (const char* gv = getenv("PHOBOS_GEMM_GROUP_M")) {   // tuning knob: row-blocks per raster band
+    const int v = atoi(gv);
+    if (v >= 1 && v <= 1024) p.group_m = v;
+  }
   p.alpha = alpha;
   p.beta = beta;
   p.C = C;
