@@ -63,6 +63,7 @@ struct Tc2Params {
   // 2: two tiles of a pair are in flight at once, each with its own producer, issuer,
   // accumulator buffer and half of the stage ring (see the kernel comment); 1: one tile
   int streams;
+  int l2hint;             // bit 0: A panels loaded evict-last; bit 1: B panels evict-first; bit 2: C_old / C streaming
 };
 
 // Work unit u of a launch -> (tile, K range).  Units [0, split_first) are whole
@@ -184,6 +185,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      // a raster band's A rows are used by every wave of the band, a B panel by one wave only
+      const uint64_t pol_a = l2_policy_evict_last(), pol_b = l2_policy_evict_first();
       for (int n = sidx; ok; n += p.streams) {
         const int u = pair + n * num_pairs;
         if (u >= num_units) break;
@@ -203,9 +206,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           }
           const uint32_t full_leader = mapa_u32(smem_u32(&full[st]), 0);
           if (leader) mbar_arrive_expect_tx(&full[st], stage_tx);  // bytes of both CTAs' loads
-          tma_load_2d_pair(sA + st * A_BYTES, &tmA, full_leader, kb * BK, row0);
-          for (int j = 0; j < nbox; j++)
-            tma_load_2d_pair(sB + st * B_BYTES + j * (BK * 128), &tmB, full_leader, col0 + j * 64, kb * BK);
+          if (p.l2hint & 1) tma_load_2d_pair_hint(sA + st * A_BYTES, &tmA, full_leader, kb * BK, row0, pol_a);
+          else tma_load_2d_pair(sA + st * A_BYTES, &tmA, full_leader, kb * BK, row0);
+          for (int j = 0; j < nbox; j++) {
+            if (p.l2hint & 2)
+              tma_load_2d_pair_hint(sB + st * B_BYTES + j * (BK * 128), &tmB, full_leader, col0 + j * 64, kb * BK, pol_b);
+            else
+              tma_load_2d_pair(sB + st * B_BYTES + j * (BK * 128), &tmB, full_leader, col0 + j * 64, kb * BK);
+          }
           if (++stage == ring) {
             stage = 0;
             phase ^= 1;
@@ -306,6 +314,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         // instruction covers 4 rows x 128 contiguous bytes; the C_old values of the
         // chunk are requested before the transpose so their latency overlaps it.
         float* pad = epi_pad + q * (32 * EPI_LD);
+        const bool cs = (p.l2hint & 4) != 0;
         const int sub_row = lane >> 3, sub_col = (lane & 7) * 4;
         const long long row_base = static_cast<long long>(mb) * (2 * BM) + static_cast<int>(rank) * BM + q * 32;
 #pragma unroll 1
@@ -316,8 +325,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
           for (int it = 0; it < 8; it++) {
             const long long rr = row_base + it * 4 + sub_row;
-            old[it] = (col_ok && rr < p.M) ? *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.C) + rr * p.ldc + col)
-                                           : make_float4(0.f, 0.f, 0.f, 0.f);
+            const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.C) + rr * p.ldc + col);
+            old[it] = (col_ok && rr < p.M) ? (cs ? __ldcs(src) : *src) : make_float4(0.f, 0.f, 0.f, 0.f);
           }
           uint32_t r[32];
           tmem_ld_32x32b_x32(t_addr + c * 32, r);
@@ -337,7 +346,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
               o.y = __fadd_rn(__fmul_rn(p.alpha, a4.y), __fmul_rn(beta, old[it].y));
               o.z = __fadd_rn(__fmul_rn(p.alpha, a4.z), __fmul_rn(beta, old[it].z));
               o.w = __fadd_rn(__fmul_rn(p.alpha, a4.w), __fmul_rn(beta, old[it].w));
-              *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.C) + rr * p.ldc + col) = o;
+              float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.C) + rr * p.ldc + col);
+              if (cs) __stcs(dst, o);
+              else *dst = o;
             }
           }
         }
@@ -514,6 +525,8 @@ int launch_gemm_tc_pair(const void* A, long long lda, const void* B, long long l
   // test: 151 against 171 clocks per 256-wide MMA).  Off by default: measured on the real
   // kernel it gains nothing at 8192^3 (1548 TFLOP/s either way) and loses at 4096^3
   // (1058 against 1150: with 3.46 tiles per pair the second stream only lengthens the tail).
+  p.l2hint = 0;
+  if (const char* hv = getenv("PHOBOS_GEMM_L2HINT")) p.l2hint = atoi(hv) & 7;
   p.streams = 1;
   if (const char* sv = getenv("PHOBOS_GEMM_STREAMS")) p.streams = (sv[0] == '2') ? 2 : 1;
   if (p.split > 1) p.streams = 1;  // the K ranges of a split tile must run one after the other
