@@ -129,7 +129,9 @@ class ClockSampler:
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(smax) if smax else None,
                 "reasons": sorted(reasons), "samples_under_load": len(power),
-                "power_w_max": max(power) if power else None}
+                "power_w_max": max(power) if power else None,
+                "sampling": "nvidia-smi every 200 ms; the clock inside a burst of tensor-core kernels is lower than "
+                            "these samples show (phobos-lang_b200/clock_trace.py samples it every 50 us)"}
 
 
 # ---------------------------------------------------------------------------------------------
