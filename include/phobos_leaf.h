@@ -159,14 +159,22 @@ PH_API int phobos_flash_attention(const PhTensor *Q, const PhTensor *K, const Ph
                                   void *stream);
 PH_API size_t phobos_flash_workspace_bytes(int32_t dtype, int64_t batch_heads, int64_t Nq, int64_t Nk, int64_t D);
 
-/* Diagnostic (no reference counterpart; the reference only has `--autotune` pins
- * "for ncu profiling", phobos-bench/src/main.rs:35-36): while a device buffer of
- * at least 2048 64-bit words is set for the current device, CTA (0,0) of every
- * flash launch records clock64 stamps of its pipeline phases in it, laid out
- * [role: softmax tile 0, softmax tile 1, MMA issuer, TMA producer][key block < 64]
- * [slot < 8].  NULL switches tracing off.  Only libraries built with
- * -DPH_FLASH_TRACE carry the stamps; others return PH_ERR_UNSUPPORTED.        */
-PH_API int phobos_flash_trace(uint64_t *device_buf, uint64_t n_words);
+/* Diagnostic (no reference counterpart; the reference derives its fp32 peak from the
+ * device's nominal clock, phobos-bench/src/report.rs:125-147): the SM clock a launch
+ * actually ran at.  One CTA of every GEMM and flash launch records how many SM cycles
+ * and how many nanoseconds of the global timer it lived; this call synchronises
+ * `stream` and returns the pair of the most recent such launch on the current device
+ * (cycles / ns = GHz).  The timer ticks in steps of up to 1 us, so the ratio is
+ * meaningful for launches of tens of microseconds and longer.                      */
+PH_API int phobos_last_launch_clock(void *stream, uint64_t *sm_cycles, uint64_t *timer_ns);
+
+/* Self-test of the bounded-wait policy (the analogue of the reference's stall detector
+ * and fetch deadline, phobos-pod/src/engine.rs:752-775, 825-828): launches one CTA that
+ * waits on a barrier nobody arrives at, with a limit of `limit_ns`.  The kernel gives up
+ * when the limit passes, records its site code and ends normally; the next
+ * phobos_device_status() call on the device then reports PH_ERR_TIMEOUT once, and the
+ * device stays usable.  Returns PH_OK when the launch was enqueued.                  */
+PH_API int phobos_selftest_bounded_wait(uint64_t limit_ns, void *stream);
 
 /* ---- kda (chunkwise gated linear attention) ------------------------------------------- *
  * One head: Q, K, V, O [N, 64] f32, G [N, 1] the per-token log forget-gate, scale on the

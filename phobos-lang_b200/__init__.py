@@ -104,7 +104,8 @@ def lib() -> ctypes.CDLL:
             "phobos_matmul_init": (c.c_int, [TP, f32, i32, vp]),
             "phobos_flash_attention": (c.c_int, [TP, TP, TP, TP, f32, i64, vp, sz, vp]),
             "phobos_flash_workspace_bytes": (sz, [i32, i64, i64, i64, i64]),
-            "phobos_flash_trace": (c.c_int, [vp, u64]),
+            "phobos_last_launch_clock": (c.c_int, [vp, c.POINTER(u64), c.POINTER(u64)]),
+            "phobos_selftest_bounded_wait": (c.c_int, [u64, vp]),
             "phobos_launch": (c.c_int, [c.c_char_p, TP, i32, SP, i32, c.POINTER(u32), c.POINTER(u32), i32, vp, sz, vp]),
             "phobos_launch_workspace_bytes": (sz, [c.c_char_p, TP, i32, i32]),
             "phobos_fill_random_host": (c.c_int, [c.POINTER(f32), u64, u64, u64, f32]),
@@ -182,6 +183,11 @@ def tensor_desc(t) -> PhTensor:
     """PhTensor for a rank-1/2 CUDA torch tensor (no copy; the caller keeps `t` alive)."""
     if not t.is_cuda:
         raise PhobosError(PH_ERR_INVALID, "tensor is not on a CUDA device")
+    import torch
+    if t.device.index != torch.cuda.current_device():
+        # the library launches on the current device and uses that device's status word
+        raise PhobosError(PH_ERR_INVALID, f"tensor lives on cuda:{t.device.index} but the current device is "
+                                          f"cuda:{torch.cuda.current_device()}")
     d = PhTensor()
     d.ptr = t.data_ptr()
     d.dtype = _torch_dtype_code(t)
@@ -317,6 +323,20 @@ def device_status(stream=None) -> int:
     w = ctypes.c_uint32(0)
     check(lib().phobos_device_status(_stream_ptr(stream), ctypes.byref(w)))
     return int(w.value)
+
+
+def last_launch_clock(stream=None) -> tuple[int, int]:
+    """(SM cycles, timer nanoseconds) one CTA of the most recent GEMM / flash launch on the current device lived;
+    cycles / ns is the SM clock in GHz during that launch.  Synchronises the stream."""
+    cyc, ns = ctypes.c_uint64(0), ctypes.c_uint64(0)
+    check(lib().phobos_last_launch_clock(_stream_ptr(stream), ctypes.byref(cyc), ctypes.byref(ns)))
+    return int(cyc.value), int(ns.value)
+
+
+def selftest_bounded_wait(limit_ns: int, stream=None) -> None:
+    """Enqueues a one-CTA kernel whose barrier wait must run out after `limit_ns`; device_status() then raises
+    PH_ERR_TIMEOUT once and the device stays usable."""
+    check(lib().phobos_selftest_bounded_wait(limit_ns, _stream_ptr(stream)))
 
 
 def device_info(device: int = 0) -> PhDeviceInfo:

@@ -15,7 +15,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 OBJ = HERE / "build"
 LIB = HERE / "libphobos_leaf.so"
-SOURCES = ["api.cu", "gemm_tc.cu", "gemm_tc2.cu", "gemm_f32.cu", "flash.cu", "elementwise.cu", "kda.cu", "tmap.cu", "noalloc.cu",
+SOURCES = ["api.cu", "gemm_tc.cu", "gemm_tc2.cu", "gemm_f32.cu", "flash.cu", "elementwise.cu", "kda.cu", "tmap.cu", "noalloc.cu", "selftest.cu",
            "host.cpp", "executor.cpp", "source.cpp", "planner.cpp", "plan_api.cpp", "wire.cpp"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall", "-Xptxas", "-v"]
@@ -69,29 +69,5 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB
 
 
-def build_probes() -> Path:
-    """Compiles the diagnostics: the pipe-rate probe (csrc/probes/pipe_probe.cu -> phobos-lang_b200/pipe_probe)
-    and the SM clock sampler (csrc/probes/clock_spy.cu -> phobos-lang_b200/libclock_spy.so)."""
-    out = HERE / "pipe_probe"
-    env = dict(os.environ)
-    env.pop("CC", None)
-    env.pop("CXX", None)
-    cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-o", str(out),
-           str(CSRC / "probes" / "pipe_probe.cu")]
-    r = subprocess.run(cmd, capture_output=True, text=True, env=env)
-    if r.returncode != 0:
-        raise RuntimeError(f"nvcc failed for pipe_probe.cu:\n{r.stdout}\n{r.stderr}")
-    spy = HERE / "libclock_spy.so"
-    cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-shared", "-Xcompiler", "-fPIC",
-           "-o", str(spy), str(CSRC / "probes" / "clock_spy.cu")]
-    r = subprocess.run(cmd, capture_output=True, text=True, env=env)
-    if r.returncode != 0:
-        raise RuntimeError(f"nvcc failed for clock_spy.cu:\n{r.stdout}\n{r.stderr}")
-    return out
-
-
 if __name__ == "__main__":
-    if "--probes" in sys.argv:
-        print(build_probes())
-    else:
-        print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

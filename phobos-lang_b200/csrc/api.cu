@@ -30,9 +30,10 @@ void clear_error() { t_err[0] = 0; }
 const char* last_error() { return t_err; }
 
 // ---- per-device state -----------------------------------------------------------
-// Word written by kernels whose bounded wait gave up.  It lives in the module's
-// device data segment; its address is looked up once per device.
-__device__ uint32_t g_status_word;
+// Diagnostic block of the device, in the module's device data segment; its address
+// is looked up once per device.  Word 0 is written by kernels whose bounded wait
+// gave up; words 2..5 hold the launch clock (two 64-bit values, see common.cuh).
+__device__ __align__(16) uint32_t g_status_word[8];
 
 struct DeviceState {
   bool ready = false;
@@ -60,7 +61,7 @@ int device_state(DeviceState** out) {
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, g_status_word);
     if (e != cudaSuccess) return fail(PH_ERR_DEVICE, "cudaGetSymbolAddress: %s", cudaGetErrorString(e));
-    e = cudaMemset(p, 0, sizeof(uint32_t));
+    e = cudaMemset(p, 0, 8 * sizeof(uint32_t));
     if (e != cudaSuccess) return fail(PH_ERR_DEVICE, "cudaMemset: %s", cudaGetErrorString(e));
     s.sm_count = prop.multiProcessorCount;
     s.cc_major = prop.major;
@@ -120,26 +121,32 @@ static int map_launch_rc(int rc, const char* what, const char* err) {
 
 static size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
 
-static int gemm_bn_override() {
-  const char* s = getenv("PHOBOS_GEMM_BN");
-  return s ? atoi(s) : 0;
+// Tensor-core GEMM dispatch: CTA pairs once the problem spans at least a quarter of a round of
+// 256 x 256 pair tiles, the 1-CTA kernel below that.
+static bool tc_uses_pairs(long long M, long long N, int sm_count) {
+  return ((M + 255) / 256) * ((N + 255) / 256) >= sm_count / 4 && M >= 256 && N >= 128;
 }
 
-// Tensor-core GEMM dispatch: CTA pairs once the problem spans at least one
-// 256-row pair tile per pair of SMs' worth of work, the 1-CTA kernel below that.
-// PHOBOS_GEMM_MODE=1 / 2 forces one of them (experiments only).
 static int launch_tc(const void* A, long long lda, const void* B, long long ldb, void* C, long long ldc, int M, int N,
-                     int K, float alpha, float beta, bool acc_f16, bool c_f16, int sm_count, uint32_t* status,
-                     cudaStream_t stream, const char** err) {
-  const char* mode = getenv("PHOBOS_GEMM_MODE");
-  bool pair = static_cast<long long>((M + 255) / 256) * ((N + 255) / 256) >= sm_count / 4 && M >= 256 && N >= 128;
-  if (mode && mode[0] == '1') pair = false;
-  if (mode && mode[0] == '2') pair = true;
-  if (pair)
-    return launch_gemm_tc_pair(A, lda, B, ldb, C, ldc, M, N, K, alpha, beta, acc_f16, c_f16, gemm_bn_override(),
-                               sm_count, status, stream, err);
-  return launch_gemm_tc(A, lda, B, ldb, C, ldc, M, N, K, alpha, beta, acc_f16, c_f16, gemm_bn_override(), sm_count,
-                        status, stream, err);
+                     int K, float alpha, float beta, bool acc_f16, bool c_f16, int sm_count, void* workspace,
+                     size_t workspace_bytes, uint32_t* status, cudaStream_t stream, const char** err) {
+  if (tc_uses_pairs(M, N, sm_count))
+    return launch_gemm_tc_pair(A, lda, B, ldb, C, ldc, M, N, K, alpha, beta, acc_f16, c_f16, sm_count, workspace,
+                               workspace_bytes, status, stream, err);
+  return launch_gemm_tc(A, lda, B, ldb, C, ldc, M, N, K, alpha, beta, acc_f16, c_f16, sm_count, status, stream, err);
+}
+
+// Bytes of the rounded f16 copies of f32-stored A [M,K] and B [K,N].
+size_t gemm_staging_bytes(long long M, long long N, long long K) {
+  return align256(static_cast<size_t>(M) * K * 2) + align256(static_cast<size_t>(K) * N * 2);
+}
+
+// SM count of the current device if one is usable, else that of a B200.
+static int sm_count_or_default() {
+  DeviceState* ds;
+  if (device_state(&ds) == PH_OK) return ds->sm_count;
+  clear_error();
+  return 148;
 }
 
 }  // namespace ph
@@ -198,9 +205,14 @@ int phobos_device_status(void* stream, uint32_t* status_out) {
 }
 
 size_t phobos_gemm_workspace_bytes(int32_t kind, int32_t a_dtype, int64_t M, int64_t N, int64_t K) {
-  if (kind == PH_GEMM_FP16TC_FP32ACC && a_dtype == PH_F32)
-    return align256(static_cast<size_t>(M) * K * 2) + align256(static_cast<size_t>(K) * N * 2);
-  return 0;
+  if (M <= 0 || N <= 0 || K <= 0 || M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return 0;
+  size_t bytes = 0;
+  if (kind == PH_GEMM_FP16TC_FP32ACC && a_dtype == PH_F32) bytes += gemm_staging_bytes(M, N, K);
+  if (kind == PH_GEMM_FP16TC_FP32ACC || kind == PH_GEMM_FP16) {
+    const int sms = sm_count_or_default();
+    if (tc_uses_pairs(M, N, sms)) bytes += gemm_tc_pair_workspace_bytes((int)M, (int)N, (int)K, sms);
+  }
+  return bytes;
 }
 
 int phobos_gemm(const PhTensor* A, const PhTensor* B, const PhTensor* C, float alpha, float beta, int32_t kind,
@@ -231,16 +243,20 @@ int phobos_gemm(const PhTensor* A, const PhTensor* B, const PhTensor* C, float a
       const void* a16 = a.base;
       const void* b16 = b.base;
       long long lda = a.ld, ldb = b.ld;
+      char* ws = static_cast<char*>(workspace);
+      size_t ws_bytes = workspace ? workspace_bytes : 0;
+      if (ws && reinterpret_cast<uintptr_t>(ws) % 256 != 0) return fail(PH_ERR_WORKSPACE, "workspace is not 256-byte aligned");
       if (a.dtype == PH_F32) {
         // the .ph signature: f32 storage, rounded RN-even to f16 when staged
-        // (phobos-lang/src/codegen/matmul.rs:2166-2231); here by a convert pass
-        const size_t need = phobos_gemm_workspace_bytes(kind, PH_F32, M, N, K);
-        if (!workspace || workspace_bytes < need)
+        // (phobos-lang/src/codegen/matmul.rs:2166-2231); here by a convert pass.
+        // Everything is validated before the first kernel touches the workspace.
+        if ((K * 2) % 16 != 0 || (N * 2) % 16 != 0)
+          return fail(PH_ERR_INVALID, "gemm_fp16tc_fp32acc: K and N must be multiples of 8");
+        const size_t need = gemm_staging_bytes(M, N, K);
+        if (!ws || ws_bytes < need)
           return fail(PH_ERR_WORKSPACE, "gemm_fp16tc_fp32acc with f32 operands needs %zu workspace bytes, got %zu", need,
-                      workspace_bytes);
-        if (reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
-          return fail(PH_ERR_WORKSPACE, "workspace is not 256-byte aligned");
-        char* wa = static_cast<char*>(workspace);
+                      ws_bytes);
+        char* wa = ws;
         char* wb = wa + align256(static_cast<size_t>(M) * K * 2);
         if ((rc = launch_f32_to_f16_2d(reinterpret_cast<const float*>(a.base), a.ld, wa, M, K, stream, &err)) ||
             (rc = launch_f32_to_f16_2d(reinterpret_cast<const float*>(b.base), b.ld, wb, K, N, stream, &err)))
@@ -249,18 +265,20 @@ int phobos_gemm(const PhTensor* A, const PhTensor* B, const PhTensor* C, float a
         b16 = wb;
         lda = K;
         ldb = N;
-        if ((K * 2) % 16 != 0 || (N * 2) % 16 != 0)
-          return fail(PH_ERR_INVALID, "gemm_fp16tc_fp32acc: K and N must be multiples of 8");
+        ws += need;          // what is left may serve the kernel's own scratch
+        ws_bytes -= need;
       }
       rc = launch_tc(a16, lda, b16, ldb, c.base, c.ld, (int)M, (int)N, (int)K, alpha, beta, false, false,
-                     ds->sm_count, ds->status, stream, &err);
+                     ds->sm_count, ws, ws_bytes, ds->status, stream, &err);
       return map_launch_rc(rc, "gemm_fp16tc_fp32acc", err);
     }
     case PH_GEMM_FP16: {
       if (a.dtype != PH_F16 || b.dtype != PH_F16 || c.dtype != PH_F16)
         return fail(PH_ERR_INVALID, "gemm_fp16 takes f16 A, B and C");
+      if (workspace && reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
+        return fail(PH_ERR_WORKSPACE, "workspace is not 256-byte aligned");
       rc = launch_tc(a.base, a.ld, b.base, b.ld, c.base, c.ld, (int)M, (int)N, (int)K, alpha, beta, true, true,
-                     ds->sm_count, ds->status, stream, &err);
+                     ds->sm_count, workspace, workspace ? workspace_bytes : 0, ds->status, stream, &err);
       return map_launch_rc(rc, "gemm_fp16", err);
     }
     default:
@@ -331,16 +349,31 @@ int phobos_flash_attention(const PhTensor* Q, const PhTensor* K, const PhTensor*
   return map_launch_rc(rc, "flash_attention", err);
 }
 
-int phobos_flash_trace(uint64_t* device_buf, uint64_t n_words) {
+int phobos_last_launch_clock(void* stream, uint64_t* sm_cycles, uint64_t* timer_ns) {
   clear_error();
-#ifndef PH_FLASH_TRACE
-  if (device_buf != nullptr)
-    return fail(PH_ERR_UNSUPPORTED, "this build has no flash trace stamps (compile with -DPH_FLASH_TRACE)");
-#endif
-  int rc = set_flash_trace(reinterpret_cast<unsigned long long*>(device_buf), n_words);
-  if (rc == -1) return fail(PH_ERR_INVALID, "flash trace buffer needs at least 2048 64-bit words");
-  if (rc) return fail(PH_ERR_DEVICE, "no current device");
+  DeviceState* ds;
+  int rc = device_state(&ds);
+  if (rc) return rc;
+  cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(PH_ERR_DEVICE, "cudaStreamSynchronize: %s", cudaGetErrorString(e));
+  unsigned long long w[2] = {0, 0};
+  e = cudaMemcpy(w, ds->status + 2, sizeof(w), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return fail(PH_ERR_DEVICE, "launch clock read: %s", cudaGetErrorString(e));
+  if (sm_cycles) *sm_cycles = w[0];
+  if (timer_ns) *timer_ns = w[1];
   return PH_OK;
+}
+
+int phobos_selftest_bounded_wait(uint64_t limit_ns, void* stream) {
+  clear_error();
+  if (limit_ns == 0 || limit_ns > 1000000000ull)
+    return fail(PH_ERR_INVALID, "selftest wait limit %llu ns is not in (0, 1 s]", (unsigned long long)limit_ns);
+  DeviceState* ds;
+  int rc = device_state(&ds);
+  if (rc) return rc;
+  const char* err = "";
+  rc = launch_selftest_wait(limit_ns, ds->status, static_cast<cudaStream_t>(stream), &err);
+  return map_launch_rc(rc, "selftest_bounded_wait", err);
 }
 
 // ---- launch by entry name ---------------------------------------------------------------

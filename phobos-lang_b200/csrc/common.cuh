@@ -1,11 +1,11 @@
 // Shared device helpers for the sm_100a leaf kernels: mbarrier, TMA, tcgen05
 // (UMMA + tensor memory) wrappers in inline PTX, and the bounded-wait policy.
 //
-// Bounded waits: every spin on an mbarrier gives up after PH_WAIT_NS of wall
-// time, records a code in the per-device status word and lets the kernel run
-// to its normal end (TMEM is freed, no trap).  A kernel therefore cannot hang
-// the GPU on a protocol bug; the host sees PH_ERR_TIMEOUT via
-// phobos_device_status().
+// Bounded waits: every spin on an mbarrier gives up after WaitCtx::limit_ns of
+// wall time (PH_WAIT_NS unless a caller asks for less), records a code in the
+// per-device status word and lets the kernel run to its normal end (TMEM is
+// freed, no trap).  A kernel therefore cannot hang the GPU on a protocol bug;
+// the host sees PH_ERR_TIMEOUT via phobos_device_status().
 #pragma once
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -16,22 +16,25 @@ namespace ph {
 // ---- status word -----------------------------------------------------------
 // One word per device (defined in api.cu, passed to every kernel by address),
 // written by kernels on a wait that ran out.
+constexpr uint64_t PH_WAIT_NS = 2000000000ull;  // 2 s per wait
+
 struct WaitCtx {
   volatile uint32_t* abort_flag;  // shared memory, one per CTA
   uint32_t* status;               // global memory, one per device
+  uint64_t limit_ns = PH_WAIT_NS;
 };
-
-constexpr uint64_t PH_WAIT_NS = 2000000000ull;  // 2 s per wait
 
 enum WaitSite : uint32_t {
   SITE_GEMM_PRODUCER_EMPTY = 0x11,
   SITE_GEMM_MMA_FULL = 0x12,
   SITE_GEMM_MMA_TMEM_EMPTY = 0x13,
   SITE_GEMM_EPI_TMEM_FULL = 0x14,
+  SITE_GEMM_FIXUP_FLAG = 0x15,
   SITE_FLASH_LOAD = 0x21,
   SITE_FLASH_MMA = 0x22,
   SITE_FLASH_SOFTMAX = 0x23,
   SITE_FLASH_EPI = 0x24,
+  SITE_SELFTEST = 0x31,
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -54,6 +57,23 @@ __device__ __forceinline__ bool elect_one() {
       "}\n"
       : "=r"(pred));
   return pred != 0;
+}
+
+// ---- launch clock ------------------------------------------------------------
+// The device's diagnostic block starts at the status word: status[0] the wait
+// status, then (8-byte aligned, at status + 2) the SM cycles and the timer
+// nanoseconds one CTA of the most recent launch lived.  The CTA that reports
+// calls launch_clock_begin() first thing and launch_clock_end() last thing.
+// The start values live in shared memory (`slot`, two 64-bit words) so that they do
+// not hold registers for the length of the kernel.
+__device__ __forceinline__ void launch_clock_begin(unsigned long long* slot) {
+  slot[1] = globaltimer_ns();
+  slot[0] = static_cast<unsigned long long>(clock64());
+}
+__device__ __forceinline__ void launch_clock_end(const unsigned long long* slot, uint32_t* status) {
+  unsigned long long* d = reinterpret_cast<unsigned long long*>(status + 2);
+  d[0] = static_cast<unsigned long long>(clock64()) - slot[0];
+  d[1] = globaltimer_ns() - slot[1];
 }
 
 // ---- mbarrier ----------------------------------------------------------------
@@ -103,7 +123,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 0xFF) == 0) {
       if (*ctx.abort_flag != 0) return false;
-      if (globaltimer_ns() - t0 > PH_WAIT_NS) {
+      if (globaltimer_ns() - t0 > ctx.limit_ns) {
         *ctx.abort_flag = site;
         atomicCAS(ctx.status, 0u, site | (blockIdx.x << 8));
         return false;

@@ -101,9 +101,10 @@ struct Node {
 struct Inflight {
   cudaEvent_t event;
   uint64_t iid;
-  bool has_wrote;
-  uint64_t wrote;
-  void* host_stage;  // pinned staging buffer to release on completion (LOAD)
+  std::vector<uint64_t> wrote;  // tiles that become resident when the event completes
+  void* host_stage;             // pinned staging buffer to release on completion (LOAD)
+  PhExecutor* served_by;        // FETCH: the peer whose tile `wrote[0]` is being copied, to be credited with a serve
+  uint64_t serve_bytes;
 };
 
 struct KernelEntry {
@@ -238,13 +239,14 @@ cudaStream_t pick_stream(PhExecutor* ex) {
   return s;
 }
 
-bool track(PhExecutor* ex, cudaStream_t s, uint64_t iid, bool has_wrote, uint64_t wrote, void* stage) {
+bool track(PhExecutor* ex, cudaStream_t s, uint64_t iid, std::vector<uint64_t> wrote, void* stage,
+           PhExecutor* served_by = nullptr, uint64_t serve_bytes = 0) {
   cudaEvent_t ev;
   if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess || cudaEventRecord(ev, s) != cudaSuccess) {
     fail_instr(ex, iid, PH_ERR_DEVICE, "event record failed");
     return false;
   }
-  ex->inflight.push_back({ev, iid, has_wrote, wrote, stage});
+  ex->inflight.push_back({ev, iid, std::move(wrote), stage, served_by, serve_bytes});
   return true;
 }
 
@@ -271,7 +273,7 @@ void do_load(PhExecutor* ex, uint64_t iid, const Node& n) {
     cudaFreeHost(stage);
     return fail_instr(ex, iid, PH_ERR_DEVICE, "LOAD: host-to-device copy failed");
   }
-  track(ex, s, iid, true, n.in.tile, stage);
+  track(ex, s, iid, {n.in.tile}, stage);
 }
 
 void do_store(PhExecutor* ex, uint64_t iid, const Node& n) {
@@ -280,6 +282,11 @@ void do_store(PhExecutor* ex, uint64_t iid, const Node& n) {
   if (t == ex->tiles.end()) return fail_instr(ex, iid, PH_ERR_STATE, "STORE of unknown tile");
   const TensorMetaOwned& m = ex->tensors[n.in.tensor];
   const size_t es = phobos_dtype_bytes(t->second.dtype);
+  // storage.rs store_f32: "store data/region length mismatch"
+  uint64_t total = 1;
+  for (int d = 0; d < n.in.region.rank; d++) total *= n.in.region.shape[d];
+  if (total != t->second.elems || m.dtype != t->second.dtype)
+    return fail_instr(ex, iid, PH_ERR_STATE, "STORE region does not match the tile");
   std::vector<char> host(t->second.elems * es);
   // device-to-host on the executor thread (engine.rs:472-473); all streams are
   // drained first because the producer may have run on any of them
@@ -300,11 +307,14 @@ bool do_fetch(PhExecutor* ex, uint64_t iid, const Node& n) {
     return true;
   }
   PhExecutor* peer = pe->second;
-  // try_lock: two executors fetching from each other must not wait on each other's lock
-  std::unique_lock<std::mutex> peer_lock(peer->mu, std::try_to_lock);
-  if (peer != ex && !peer_lock.owns_lock()) return false;
+  // try_lock: two executors fetching from each other must not wait on each other's lock.
+  // A fetch from this executor itself already runs under its own lock.
+  std::unique_lock<std::mutex> peer_lock(peer->mu, std::defer_lock);
+  if (peer != ex && !peer_lock.try_lock()) return false;
   auto src = peer->tiles.find(n.in.tile);
-  if (src == peer->tiles.end() || !src->second.resident) return false;  // served once resident (engine.rs:698-705)
+  // served once resident (engine.rs:698-705); a tile is marked resident only after the event of its
+  // producer has completed, so its bytes are final and no synchronisation with the peer's streams is needed
+  if (src == peer->tiles.end() || !src->second.resident) return false;
   auto dst = ex->tiles.find(n.in.tile);
   if (dst == ex->tiles.end()) {
     fail_instr(ex, iid, PH_ERR_STATE, "FETCH into unknown tile");
@@ -316,26 +326,15 @@ bool do_fetch(PhExecutor* ex, uint64_t iid, const Node& n) {
     return true;
   }
   cudaStream_t s = pick_stream(ex);
-  {
-    // the producer of the source tile may still be running on the peer's streams
-    DeviceGuard g(peer->device);
-    cudaDeviceSynchronize();
-  }
   cudaError_t e = cudaMemcpyPeerAsync(reinterpret_cast<void*>(dst->second.slab.addr), ex->device,
                                       reinterpret_cast<void*>(src->second.slab.addr), peer->device, bytes, s);
   if (e != cudaSuccess) {
     fail_instr(ex, iid, PH_ERR_DEVICE, std::string("FETCH: ") + cudaGetErrorString(e));
     return true;
   }
-  // the serve counts once the data has left the source tile (the reference
-  // serves a finished device-to-host copy): the home may FREE it right after
-  if (cudaStreamSynchronize(s) != cudaSuccess) {
-    fail_instr(ex, iid, PH_ERR_DEVICE, "FETCH: copy did not complete");
-    return true;
-  }
-  src->second.serves++;
-  peer->served_bytes += bytes;
-  track(ex, s, iid, true, n.in.tile, nullptr);
+  // Event-tracked like COMPUTE.  The serve is credited when the copy has completed (the reference
+  // serves a finished device-to-host copy), so the home cannot FREE the tile under the copy.
+  track(ex, s, iid, {n.in.tile}, nullptr, peer, bytes);
   return true;
 }
 
@@ -343,8 +342,7 @@ void do_compute(PhExecutor* ex, uint64_t iid, const Node& n) {
   auto k = ex->kernels.find(n.in.kernel);
   if (k == ex->kernels.end()) return fail_instr(ex, iid, PH_ERR_STATE, "COMPUTE of unknown kernel id");
   std::vector<PhTensor> tensors(n.args.size());
-  bool has_wrote = false;
-  uint64_t wrote = 0;
+  std::vector<uint64_t> wrote;
   for (size_t i = 0; i < n.args.size(); i++) {
     auto t = ex->tiles.find(n.args[i].tile);
     if (t == ex->tiles.end()) return fail_instr(ex, iid, PH_ERR_STATE, "COMPUTE argument is an unknown tile");
@@ -361,10 +359,7 @@ void do_compute(PhExecutor* ex, uint64_t iid, const Node& n) {
       d.strides[r] = stride;
       stride *= (int64_t)tb.shape[r];
     }
-    if (n.args[i].mode == PH_WRITE || n.args[i].mode == PH_RMW) {
-      has_wrote = true;
-      wrote = n.args[i].tile;
-    }
+    if (n.args[i].mode == PH_WRITE || n.args[i].mode == PH_RMW) wrote.push_back(n.args[i].tile);
   }
   // a kernel that comes with an `<name>_init` leaf is the accumulate step of a chain
   int32_t hint = k->second.kind_hint;
@@ -393,7 +388,7 @@ void do_compute(PhExecutor* ex, uint64_t iid, const Node& n) {
                          (int32_t)n.scalars.size(), n.in.grid, n.in.cta, hint, ex->workspace,
                          ex->workspace_bytes, s);
   if (rc) return fail_instr(ex, iid, rc, std::string("COMPUTE: ") + last_error());
-  track(ex, s, iid, has_wrote, wrote, nullptr);
+  track(ex, s, iid, std::move(wrote), nullptr);
 }
 
 void issue(PhExecutor* ex, uint64_t iid) {
@@ -429,8 +424,20 @@ bool poll_inflight(PhExecutor* ex) {
       i++;
       continue;
     }
-    Inflight f = ex->inflight[i];
-    ex->inflight[i] = ex->inflight.back();
+    if (q == cudaSuccess && ex->inflight[i].served_by != nullptr) {
+      // a finished FETCH: credit the home with the serve (under its lock; try again next round if it is busy)
+      PhExecutor* home = ex->inflight[i].served_by;
+      std::unique_lock<std::mutex> home_lock(home->mu, std::defer_lock);
+      if (home != ex && !home_lock.try_lock()) {
+        i++;
+        continue;
+      }
+      auto src = home->tiles.find(ex->inflight[i].wrote[0]);
+      if (src != home->tiles.end()) src->second.serves++;
+      home->served_bytes += ex->inflight[i].serve_bytes;
+    }
+    Inflight f = std::move(ex->inflight[i]);
+    ex->inflight[i] = std::move(ex->inflight.back());
     ex->inflight.pop_back();
     cudaEventDestroy(f.event);
     if (f.host_stage) cudaFreeHost(f.host_stage);
@@ -439,8 +446,8 @@ bool poll_inflight(PhExecutor* ex) {
       fail_instr(ex, f.iid, PH_ERR_DEVICE, std::string("device error: ") + cudaGetErrorString(q));
       continue;
     }
-    if (f.has_wrote) {
-      auto t = ex->tiles.find(f.wrote);
+    for (uint64_t w : f.wrote) {
+      auto t = ex->tiles.find(w);
       if (t != ex->tiles.end()) t->second.resident = true;
     }
     complete(ex, f.iid);
@@ -541,13 +548,19 @@ int phobos_executor_connect_peer(PhExecutor* ex, uint32_t node_id, PhExecutor* p
 int phobos_executor_issue(PhExecutor* ex, const PhInstr* instrs, int32_t n) {
   clear_error();
   if (!ex || (n > 0 && !instrs)) return fail(PH_ERR_INVALID, "null argument");
-  // add nodes, then wire dependency counters (engine.rs:297-322)
+  // the whole segment is validated before any of it enters the table
   for (int32_t i = 0; i < n; i++) {
     const PhInstr& in = instrs[i];
     if (in.op == PH_OP_ALLOC && (in.shape_rank < 1 || in.shape_rank > 2))
       return fail(PH_ERR_UNSUPPORTED, "instr %llu: ALLOC rank %d (1 or 2 supported)", (unsigned long long)in.iid, in.shape_rank);
     if (in.op == PH_OP_ALLOC && phobos_dtype_bytes(in.data_type) == 0)
       return fail(PH_ERR_INVALID, "instr %llu: ALLOC of unknown element type %d", (unsigned long long)in.iid, in.data_type);
+    if ((in.n_deps > 0 && !in.deps) || (in.n_args > 0 && !in.args) || (in.n_scalars > 0 && !in.scalars))
+      return fail(PH_ERR_INVALID, "instr %llu: a list has a count but no pointer", (unsigned long long)in.iid);
+  }
+  // add nodes, then wire dependency counters (engine.rs:297-322)
+  for (int32_t i = 0; i < n; i++) {
+    const PhInstr& in = instrs[i];
     Node nd;
     nd.in = in;
     if (in.n_deps > 0 && in.deps) nd.deps.assign(in.deps, in.deps + in.n_deps);

@@ -24,25 +24,27 @@
 //   warp 8     TMA producer: Q once, then K and V blocks of 128 keys through one
 //              ring of five slots (a block takes thousands of clocks to land while
 //              the MMAs saturate shared memory, so the ring runs two blocks ahead)
-//   warps 9,10 tcgen05.mma issuers, one per query tile: S_i = Q_i K^T into tensor
-//              memory, then O_i += P_i V with P_i read from tensor memory (it
-//              overwrites S_i).  They take strict turns, so the two tiles keep
-//              ping-ponging, but each issuer does the barrier waits of its next
-//              batch while the other one issues (a tcgen05.mma blocks its thread
-//              until the pipe accepts it; two free-running issuers fell into
-//              lockstep and were 20% slower)
-//   warp 11    idle (completes the third warpgroup)
-// Tensor memory columns: S0 | S1 | O0 | O1.
+//   warp 9     tcgen05.mma issuer (one thread) for both tiles, in a fixed order per
+//              key block j: O_0 += P_0(j) V_j, S_0 = Q_0 K_{j+1}^T, O_1 += P_1(j) V_j,
+//              S_1 = Q_1 K_{j+1}^T.  The fixed order is what keeps the two tiles half
+//              a period apart (two free-running issuers fall into lockstep, and then
+//              both tiles' exponentials compete for the MUFU unit at the same time).
+//   warps 10,11 idle (complete the third warpgroup)
+// Tensor memory columns: S0 | S1 | O0 | O1.  P_i (f16) overwrites the low half of
+// S_i and is the A operand of O_i += P_i V straight from tensor memory.
+//
+// Hand-over of P in slices: a softmax thread holds its whole row of S in registers,
+// and writes P back in P_SLICES slices of 128 / P_SLICES keys, each with its own
+// mbarrier.  The issuer starts the MMAs of a slice as soon as that slice is there, so
+// all but the last slice's share of O += P V runs while the softmax warps are still
+// busy with later exponentials; only the last slice and the next S = Q K^T remain on
+// the dependency chain S(j) -> P(j) -> S(j+1) of a tile.
 //
 // Exponentials: a 128x128 score tile needs 16384 exp2; the MUFU unit delivers 16
-// per clock per SM, i.e. 1024 clocks per tile, exactly what the tensor core needs
-// for the tile's two MMAs.  EMU of every 8 column pairs can therefore be evaluated
-// on the FMA pipes instead: 2^x = 2^n * p(f), n = round(x), f = x - n in
-// [-0.5, 0.5], p a cubic with relative error 7.5e-5 (P is rounded to f16, eps
-// 4.9e-4, right after).  The default is EMU = 0: the packed polynomial costs about
-// 30 issue clocks per pair against 16 MUFU clocks, and was measured slower for
-// every mix.  The scale/subtract, the polynomial and the row sums use packed
-// f32x2 instructions to halve their issue slots.
+// per clock per SM, i.e. 1024 clocks per tile, the same order as the tensor core's
+// time for the tile's two MMAs, so the two units have to overlap: that is what the
+// two-tile ping-pong is for.  The scale/subtract and the row sums use packed f32x2
+// instructions to halve their issue slots.
 #include <cuda.h>
 
 #include <cstdlib>
@@ -56,6 +58,11 @@ namespace {
 constexpr int QT = 128;        // query rows per tile
 constexpr int KB = 128;        // keys per block
 constexpr int FL_THREADS = 384;
+#ifndef PH_FLASH_P_SLICES
+#define PH_FLASH_P_SLICES 4
+#endif
+constexpr int P_SLICES = PH_FLASH_P_SLICES;   // hand-over pieces of a P block (1, 2, 4 or 8)
+constexpr int SLICE_KEYS = KB / P_SLICES;     // keys per piece: 16, 32, 64 or 128
 constexpr float RESCALE_TAU = 8.0f;          // log2 units
 constexpr float M_INIT = -65504.0f * 1.4426950408889634f;  // the .ph's -65504 in log2 units
 
@@ -66,7 +73,7 @@ struct FCfg {
   static constexpr int KV_BYTES = KB * D * 2;
   static constexpr int HALF_BYTES = 128 * 128;        // one [128 rows x 64 f16] box
   static constexpr int RING = 5;                      // K/V blocks in flight (shared ring)
-  static constexpr int SMEM_BYTES = 2 * QTILE_BYTES + RING * KV_BYTES + 1024 + 256;
+  static constexpr int SMEM_BYTES = 2 * QTILE_BYTES + RING * KV_BYTES + 1024 + 512;
   static constexpr int TMEM_COLS = 512;
   static constexpr int S_COL0 = 0;                    // S_i at i*128
   static constexpr int O_COL0 = 256;                  // O_i at 256 + i*D
@@ -79,16 +86,7 @@ struct FlashParams {
   int negate_q;       // scale < 0: negate Q inside the MMA instead
   void* O;            // [BH][Nq][D]
   uint32_t* status;
-  unsigned long long* trace;  // optional: clock stamps of CTA (0,0), see phobos_flash_trace
 };
-
-constexpr int TRACE_MAX_J = 64, TRACE_SLOTS = 8;
-__device__ __forceinline__ void stamp(unsigned long long* buf, int role, int j, int slot) {
-#ifdef PH_FLASH_TRACE
-  if (buf != nullptr && j < TRACE_MAX_J) buf[(role * TRACE_MAX_J + j) * TRACE_SLOTS + slot] = clock64();
-#endif
-}
-unsigned long long* g_trace_buf[64] = {};
 
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
@@ -101,16 +99,33 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
   return r;
 }
 
-constexpr int EXP_F16X2 = 9;  // value of the EMU template parameter that selects the f16x2 exponential
-__device__ __forceinline__ uint32_t ex2_f16x2(uint32_t x) {
-  uint32_t y;
-  asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
-  return y;
-}
-__device__ __forceinline__ uint32_t hadd2_bits(uint32_t a, uint32_t b) {
-  uint32_t y;
-  asm("add.rn.f16x2 %0, %1, %2;" : "=r"(y) : "r"(a), "r"(b));
-  return y;
+// N consecutive 32-bit tensor-memory columns of this thread's lane, from registers.
+template <int N>
+__device__ __forceinline__ void tmem_st_slice(uint32_t taddr, const uint32_t (&r)[N]) {
+  static_assert(N == 8 || N == 16 || N == 32 || N == 64, "slice width");
+  if constexpr (N == 8) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(r[0]),
+                 "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+  } else if constexpr (N == 16) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+  } else if constexpr (N == 32) {
+    tmem_st_32x32b_x32(taddr, r);
+  } else {
+    uint32_t lo[32], hi[32];
+#pragma unroll
+    for (int e = 0; e < 32; e++) {
+      lo[e] = r[e];
+      hi[e] = r[32 + e];
+    }
+    tmem_st_32x32b_x32(taddr, lo);
+    tmem_st_32x32b_x32(taddr + 32, hi);
+  }
 }
 __device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
   float2 d;
@@ -133,26 +148,7 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
   return d;
 }
-// 2^x for a pair on the FMA pipes (x <= ~8; clamped below at -126).
-__device__ __forceinline__ float2 exp2_poly2(float2 x) {
-  constexpr float MAGIC = 12582912.0f;  // 1.5 * 2^23: adding it rounds to the nearest integer
-  x.x = fmaxf(x.x, -126.0f);
-  x.y = fmaxf(x.y, -126.0f);
-  const float2 t = fadd2(x, make_float2(MAGIC, MAGIC));
-  const float2 n = fadd2(t, make_float2(-MAGIC, -MAGIC));
-  const float2 f = fadd2(x, make_float2(-n.x, -n.y));
-  float2 q = ffma2(make_float2(0.055171653628349304f, 0.055171653628349304f), f,
-                   make_float2(0.2426111251115799f, 0.2426111251115799f));
-  q = ffma2(q, f, make_float2(0.6932609677314758f, 0.6932609677314758f));
-  q = ffma2(q, f, make_float2(0.9999280571937561f, 0.9999280571937561f));
-  // the integer part sits in the low bits of t: shifting it into the exponent field adds n to the exponent
-  float2 r;
-  r.x = __int_as_float(__float_as_int(q.x) + (__float_as_int(t.x) << 23));
-  r.y = __int_as_float(__float_as_int(q.y) + (__float_as_int(t.y) << 23));
-  return r;
-}
-
-template <int D, bool OUT_F32, int EMU>
+template <int D, bool OUT_F32>
 __global__ void __launch_bounds__(FL_THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, FlashParams p) {
@@ -169,10 +165,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* kv_full = bars + 1;            // RING
   uint64_t* kv_empty = bars + 1 + RING;    // RING
   uint64_t* s_full = bars + 1 + 2 * RING;  // 2 (per query tile)
-  uint64_t* p_full = s_full + 2;           // 2
-  uint64_t* o_done = s_full + 4;           // 2
-  uint64_t* turn = s_full + 6;             // 2 (issuer hand-off)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 8);
+  uint64_t* o_done = s_full + 2;           // 2
+  uint64_t* p_full = s_full + 4;           // 2 x P_SLICES: [tile][slice]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(p_full + 2 * P_SLICES);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -181,19 +176,22 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int head = blockIdx.y;
   const int q_row0 = blockIdx.x * (2 * QT);
   const int nkb = p.n_kblocks;
+  // one CTA in the middle of the grid reports the SM clock it saw
+  const bool clock_cta = threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == (gridDim.y >> 1);
+  __shared__ unsigned long long clock_slot[2];
+  if (clock_cta) launch_clock_begin(clock_slot);
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < RING; s++) {
       mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], 2);  // released by both issuers
+      mbar_init(&kv_empty[s], 1);
     }
     for (int s = 0; s < 2; s++) {
       mbar_init(&s_full[s], 1);
-      mbar_init(&p_full[s], 4);    // one arrival per softmax warp
       mbar_init(&o_done[s], 1);
-      mbar_init(&turn[s], 1);
     }
+    for (int s = 0; s < 2 * P_SLICES; s++) mbar_init(&p_full[s], 4);  // one arrival per softmax warp
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tmQ);
@@ -211,7 +209,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
   if (warp >= 8) {
   // the third warpgroup hands registers to the softmax warpgroups
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 120;");
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
   if (warp == 8) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
@@ -219,15 +217,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       for (int i = 0; i < 2; i++)
         for (int h = 0; h < C_::HALVES; h++)
           tma_load_3d(sQ + i * C_::QTILE_BYTES + h * C_::HALF_BYTES, &tmQ, q_full, h * 64, q_row0 + i * QT, head);
-      unsigned long long* tb = (blockIdx.x == 0 && blockIdx.y == 0) ? p.trace : nullptr;
       int slot = 0;
       uint32_t par = 1;  // parity that a never-used slot's `empty` barrier passes
       for (int n = 0; n < 2 * nkb; n++) {
         const int j = n >> 1;
         const bool is_v = (n & 1) != 0;
-        stamp(tb, 3, j, is_v ? 2 : 0);
         if (!mbar_wait(&kv_empty[slot], par, SITE_FLASH_LOAD, wctx)) break;
-        stamp(tb, 3, j, is_v ? 3 : 1);
         mbar_arrive_expect_tx(&kv_full[slot], C_::KV_BYTES);
         for (int h = 0; h < C_::HALVES; h++)
           tma_load_3d(sKV + slot * C_::KV_BYTES + h * C_::HALF_BYTES, is_v ? &tmV : &tmK, &kv_full[slot], h * 64,
@@ -238,8 +233,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       }
     }
-  } else if (warp <= 10) {
-    // ------------------------------ MMA issuers (warp 9: tile 0, warp 10: tile 1) ---
+  } else if (warp == 9) {
+    // ------------------------------ MMA issuer (both tiles) ---------------------------
     if (lane == 0) {
       // S = Q K^T : M=128 (queries), N=128 (keys), both operands K-major
       const uint32_t idesc_s = umma_idesc_f16(QT, KB, true, false, false) | (p.negate_q ? (1u << 13) : 0u);
@@ -260,12 +255,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           umma_f16_ss(d, qd + off, kd + off, idesc_s, kk != 0 ? 1u : 0u);
         }
       };
-      auto issue_pv = [&](int i, int slot, bool accumulate) {
+      // the MMAs of P slice `sl` (keys sl*SLICE_KEYS ...): 16 keys each
+      auto issue_pv_slice = [&](int i, int slot, int sl, bool accumulate) {
         const uint64_t vd = v_desc0 + static_cast<uint64_t>(slot * (C_::KV_BYTES >> 4));
         const uint32_t d = tmem_base + C_::O_COL0 + i * D;
         const uint32_t pa = tmem_base + C_::S_COL0 + i * 128;  // P overwrote S, 2 f16 per column
 #pragma unroll
-        for (int kk = 0; kk < KB / 16; kk++) {
+        for (int k2 = 0; k2 < SLICE_KEYS / 16; k2++) {
+          const int kk = sl * (SLICE_KEYS / 16) + k2;
           // V block: [128 keys][64 d] per half; 8-key atoms 1024 B apart, halves HALF_BYTES apart;
           // a step of 16 keys is 2048 B
           umma_f16_ts(d, pa + kk * 8, vd + static_cast<uint64_t>(kk * (2048 >> 4)), idesc_o,
@@ -281,23 +278,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           cpar ^= 1;
         }
       };
-      // Issuer warp 9 owns query tile 0, warp 10 tile 1.  They take turns: while
-      // one issues its 16 MMAs (each tcgen05.mma blocks its thread until the pipe
-      // accepts it, ~96 clocks), the other performs the barrier waits of its next
-      // batch, so the tensor pipe never idles behind a wait.  turn[t] is arrived by
-      // the other issuer when its batch is issued.
-      const int i = warp - 9;
       bool ok = mbar_wait(q_full, 0, SITE_FLASH_MMA, wctx) && mbar_wait(&kv_full[cur], cpar, SITE_FLASH_MMA, wctx);
       if (ok) {
         tc_fence_after_sync();
-        issue_s(i, cur);
-        umma_commit(&s_full[i]);
+        issue_s(0, cur);
+        umma_commit(&s_full[0]);
+        issue_s(1, cur);
+        umma_commit(&s_full[1]);
         umma_commit(&kv_empty[cur]);
         advance();
       }
-      unsigned long long* tb = (blockIdx.x == 0 && blockIdx.y == 0 && i == 0) ? p.trace : nullptr;
       for (int j = 0; j < nkb && ok; j++) {
-        stamp(tb, 2, j, 0);
         const int vs = cur;
         if (!mbar_wait(&kv_full[vs], cpar, SITE_FLASH_MMA, wctx)) break;
         advance();
@@ -307,30 +298,33 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           if (!mbar_wait(&kv_full[ks], cpar, SITE_FLASH_MMA, wctx)) break;
           advance();
         }
-        // my turn: tile 0 goes first in every round (its barrier passes once before any arrival)
-        if (!mbar_wait(&turn[i], i == 0 ? ((j & 1) ^ 1) : (j & 1), SITE_FLASH_MMA, wctx)) break;
-        stamp(tb, 2, j, 1);
-        // P_i is the late input: everything else has been waited for by now
-        if (!mbar_wait(&p_full[i], j & 1, SITE_FLASH_MMA, wctx)) break;
-        stamp(tb, 2, j, 2);
-        tc_fence_after_sync();
-        issue_pv(i, vs, j > 0);
-        umma_commit(&kv_empty[vs]);
-        if (more) {
-          issue_s(i, ks);
-          umma_commit(&s_full[i]);
-          umma_commit(&kv_empty[ks]);
-        } else {
-          umma_commit(&o_done[i]);
+#pragma unroll
+        for (int i = 0; i < 2 && ok; i++) {
+#pragma unroll
+          for (int sl = 0; sl < P_SLICES; sl++) {
+            if (!mbar_wait(&p_full[i * P_SLICES + sl], j & 1, SITE_FLASH_MMA, wctx)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+            issue_pv_slice(i, vs, sl, j > 0);
+          }
+          if (!ok) break;
+          if (i == 1) umma_commit(&kv_empty[vs]);
+          if (more) {
+            issue_s(i, ks);
+            umma_commit(&s_full[i]);
+            if (i == 1) umma_commit(&kv_empty[ks]);
+          } else {
+            umma_commit(&o_done[i]);
+          }
         }
-        mbar_arrive(&turn[i ^ 1]);
-        stamp(tb, 2, j, 3);
       }
     }
   }
   } else {
     // ------------------------------ softmax / correction / epilogue ---------------
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 192;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
     const int i = warp >> 2;       // query tile
     const int q = warp & 3;        // TMEM lane quarter
     const int row_in_tile = q * 32 + lane;
@@ -342,9 +336,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     float m2 = M_INIT, l = 0.0f;
     bool ok = true;
 
-    unsigned long long* tb = (blockIdx.x == 0 && blockIdx.y == 0 && q == 0 && lane == 0) ? p.trace : nullptr;
     for (int j = 0; j < nkb; j++) {
-      stamp(tb, i, j, 0);
       // the vote keeps the warp together: the TMEM loads below are warp-collective
       if (!PH_WARP_WAIT(&s_full[i], j & 1, SITE_FLASH_SOFTMAX, wctx)) {
         ok = false;
@@ -354,9 +346,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       uint32_t sr[4][32];
 #pragma unroll
       for (int cc = 0; cc < 4; cc++) tmem_ld_32x32b_x32(s_addr + cc * 32, sr[cc]);
-      stamp(tb, i, j, 1);
       tmem_ld_wait();
-      stamp(tb, i, j, 2);
       const int valid = p.Nk - j * KB;  // keys of this block that exist
       if (valid < KB) {
 #pragma unroll
@@ -396,71 +386,35 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           if (need) m2 = mnew;
         }
       }
-      stamp(tb, i, j, 3);
       const float2 c2 = make_float2(c, c), neg_m2 = make_float2(-m2, -m2);
-      uint32_t pk[2][32];
-      if constexpr (EMU == EXP_F16X2) {
-        // Two exponentials per MUFU operation, in f16: the argument pair is rounded to
-        // f16x2 and ex2.approx.f16x2 returns the pair of probabilities already in the
-        // f16x2 form the P operand needs.  The row sum adds these f16 values (so O and l
-        // see the same p) in eight short f16x2 chains that are widened to f32 at the end.
-        uint32_t hs[8];
+      float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
 #pragma unroll
-        for (int a8 = 0; a8 < 8; a8++) hs[a8] = 0u;
+      for (int sl = 0; sl < P_SLICES; sl++) {
+        constexpr int SLICE_REGS = SLICE_KEYS / 2;   // f16 pairs per slice
+        uint32_t pk[SLICE_REGS];
 #pragma unroll
-        for (int cc = 0; cc < 4; cc++) {
-#pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            const float2 x = ffma2(make_float2(__uint_as_float(sr[cc][e]), __uint_as_float(sr[cc][e + 1])), c2, neg_m2);
-            uint32_t ph = ex2_f16x2(pack_f16x2(x.x, x.y));
-            if (valid < KB) {  // keys past the end contribute nothing
-              if (cc * 32 + e >= valid) ph &= 0xFFFF0000u;
-              if (cc * 32 + e + 1 >= valid) ph &= 0x0000FFFFu;
-            }
-            hs[(e >> 1) & 7] = hadd2_bits(hs[(e >> 1) & 7], ph);
-            pk[cc >> 1][(cc & 1) * 16 + (e >> 1)] = ph;
+        for (int e = 0; e < SLICE_KEYS; e += 2) {
+          const int col = sl * SLICE_KEYS + e;      // column inside the key block
+          const int cc = col >> 5, ce = col & 31;
+          const float2 x = ffma2(make_float2(__uint_as_float(sr[cc][ce]), __uint_as_float(sr[cc][ce + 1])), c2, neg_m2);
+          float2 pr;
+          pr.x = ex2_approx(x.x);
+          pr.y = ex2_approx(x.y);
+          if (valid < KB) {  // keys past the end contribute nothing
+            if (col >= valid) pr.x = 0.0f;
+            if (col + 1 >= valid) pr.y = 0.0f;
           }
+          if ((e & 2) == 0) la = fadd2(la, pr);
+          else lb = fadd2(lb, pr);
+          pk[e >> 1] = pack_f16x2(pr.x, pr.y);
         }
-        float sum = 0.0f;
-#pragma unroll
-        for (int a8 = 0; a8 < 8; a8++) {
-          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hs[a8]));
-          sum += f.x + f.y;
-        }
-        l += sum;
-      } else {
-        float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
-#pragma unroll
-        for (int cc = 0; cc < 4; cc++) {
-#pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            const float2 x = ffma2(make_float2(__uint_as_float(sr[cc][e]), __uint_as_float(sr[cc][e + 1])), c2, neg_m2);
-            float2 pr;
-            if (((e >> 1) & 7) < EMU) {
-              pr = exp2_poly2(x);
-            } else {
-              pr.x = ex2_approx(x.x);
-              pr.y = ex2_approx(x.y);
-            }
-            if (valid < KB) {  // keys past the end contribute nothing
-              if (cc * 32 + e >= valid) pr.x = 0.0f;
-              if (cc * 32 + e + 1 >= valid) pr.y = 0.0f;
-            }
-            if ((e & 2) == 0) la = fadd2(la, pr);
-            else lb = fadd2(lb, pr);
-            pk[cc >> 1][(cc & 1) * 16 + (e >> 1)] = pack_f16x2(pr.x, pr.y);
-          }
-        }
-        l += (la.x + la.y) + (lb.x + lb.y);
+        tmem_st_slice<SLICE_REGS>(s_addr + sl * SLICE_REGS, pk);
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[i * P_SLICES + sl]);
       }
-      stamp(tb, i, j, 4);
-      tmem_st_32x32b_x32(s_addr, pk[0]);
-      tmem_st_32x32b_x32(s_addr + 32, pk[1]);
-      tmem_st_wait();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[i]);
-      stamp(tb, i, j, 5);
+      l += (la.x + la.y) + (lb.x + lb.y);
     }
 
     if (ok && PH_WARP_WAIT(&o_done[i], 0, SITE_FLASH_EPI, wctx)) {
@@ -511,13 +465,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   __syncthreads();
   tc_fence_after_sync();
   if (warp == 9) tmem_dealloc(tmem_base, C_::TMEM_COLS);
+  if (clock_cta) launch_clock_end(clock_slot, p.status);
 }
 
-template <int D, bool OUT_F32, int EMU>
+template <int D, bool OUT_F32>
 cudaError_t launch_d(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const FlashParams& p,
                      long long batch_heads, cudaStream_t stream) {
   using C_ = FCfg<D>;
-  auto kern = flash_fwd_kernel<D, OUT_F32, EMU>;
+  auto kern = flash_fwd_kernel<D, OUT_F32>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::SMEM_BYTES);
   if (e != cudaSuccess) return e;
   dim3 grid((p.Nq + 2 * QT - 1) / (2 * QT), static_cast<unsigned>(batch_heads));
@@ -526,19 +481,6 @@ cudaError_t launch_d(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUten
 }
 
 }  // namespace
-
-// Diagnostic: while a buffer is set for the current device, CTA (0,0) of every
-// flash launch writes clock64 stamps of its softmax and MMA phases into it
-// ([role 0..3][key block < 64][slot < 8] 64-bit words).  nullptr switches it off.
-// The stamps are compiled in only with -DPH_FLASH_TRACE (they cost the MMA issuer
-// thread about 4% otherwise).
-int set_flash_trace(unsigned long long* device_buf, unsigned long long words) {
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -3;
-  if (device_buf != nullptr && words < 4ull * TRACE_MAX_J * TRACE_SLOTS) return -1;
-  g_trace_buf[dev] = device_buf;
-  return 0;
-}
 
 int launch_flash_f16(const void* Q, const void* K, const void* V, void* O, int out_f32, long long batch_heads,
                      int Nq, int Nk, int D, float scale, int sm_count, uint32_t* status, cudaStream_t stream,
@@ -568,26 +510,13 @@ int launch_flash_f16(const void* Q, const void* K, const void* V, void* O, int o
   p.negate_q = scale < 0.0f ? 1 : 0;
   p.O = O;
   p.status = status;
-  {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    p.trace = (dev >= 0 && dev < 64) ? g_trace_buf[dev] : nullptr;
-  }
-  // column pairs per 8 evaluated by the polynomial; PHOBOS_FLASH_EMU overrides it (experiments only)
-  int emu = 0;
-  if (const char* ev = getenv("PHOBOS_FLASH_EMU")) emu = atoi(ev);
   cudaError_t e;
-  if (D == 128 && !out_f32) {
-    e = emu == 9 ? launch_d<128, false, EXP_F16X2>(tmQ, tmK, tmV, p, batch_heads, stream)
-        : emu == 2 ? launch_d<128, false, 2>(tmQ, tmK, tmV, p, batch_heads, stream)
-        : emu == 4 ? launch_d<128, false, 4>(tmQ, tmK, tmV, p, batch_heads, stream)
-        : emu == 3 ? launch_d<128, false, 3>(tmQ, tmK, tmV, p, batch_heads, stream)
-                   : launch_d<128, false, 0>(tmQ, tmK, tmV, p, batch_heads, stream);
-  } else if (D == 128) {
-    e = launch_d<128, true, 0>(tmQ, tmK, tmV, p, batch_heads, stream);
+  if (D == 128) {
+    e = out_f32 ? launch_d<128, true>(tmQ, tmK, tmV, p, batch_heads, stream)
+                : launch_d<128, false>(tmQ, tmK, tmV, p, batch_heads, stream);
   } else {
-    e = out_f32 ? launch_d<64, true, 0>(tmQ, tmK, tmV, p, batch_heads, stream)
-                : launch_d<64, false, 0>(tmQ, tmK, tmV, p, batch_heads, stream);
+    e = out_f32 ? launch_d<64, true>(tmQ, tmK, tmV, p, batch_heads, stream)
+                : launch_d<64, false>(tmQ, tmK, tmV, p, batch_heads, stream);
   }
   if (e != cudaSuccess) {
     *err = cudaGetErrorString(e);

@@ -82,6 +82,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const WaitCtx wctx{abort_flag, p.status};
+  __shared__ unsigned long long clock_slot[2];
+  const bool clock_cta = threadIdx.x == 0 && blockIdx.x == 0;
+  if (clock_cta) launch_clock_begin(clock_slot);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) {
@@ -268,6 +271,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   __syncthreads();
   tc_fence_after_sync();
   if (warp == 1) tmem_dealloc(tmem_base, C_::TMEM_COLS);
+  if (clock_cta) launch_clock_end(clock_slot, p.status);
 }
 
 }  // namespace
@@ -289,7 +293,7 @@ static cudaError_t launch_cfg(const CUtensorMap& tmA, const CUtensorMap& tmB, Tc
 
 // A: [M,K] f16 row-major (lda), B: [K,N] f16 row-major (ldb), C: [M,N] f32 or f16 (ldc).
 int launch_gemm_tc(const void* A, long long lda, const void* B, long long ldb, void* C, long long ldc, int M, int N,
-                   int K, float alpha, float beta, bool acc_f16, bool c_f16, int bn_override, int sm_count,
+                   int K, float alpha, float beta, bool acc_f16, bool c_f16, int sm_count,
                    uint32_t* status, cudaStream_t stream, const char** err) {
   CUtensorMap tmA, tmB;
   if (!make_tmap_2d(&tmA, A, TMAP_F16, M, K, lda, BM, BK, TMAP_SWIZZLE_128B) ||
@@ -306,8 +310,8 @@ int launch_gemm_tc(const void* A, long long lda, const void* B, long long ldb, v
   p.C = C;
   p.ldc = ldc;
   p.status = status;
-  int bn = bn_override;
-  if (bn != 64 && bn != 128 && bn != 256) {
+  int bn;
+  {
     // widest tile that still fills the machine in whole waves reasonably well
     auto waste = [&](int b) {
       long long tiles = static_cast<long long>((M + BM - 1) / BM) * ((N + b - 1) / b);

@@ -250,11 +250,21 @@ PhJob* parse_job_text(const std::string& text, const std::string& path, const ch
 int byte_spans(const uint64_t* tensor_shape, int32_t tensor_rank, const PhRegion* region, size_t es,
                std::vector<std::pair<uint64_t, uint64_t>>* spans) {
   if (region->rank == 1) {
+    uint64_t total = 1;
+    for (int32_t d = 0; d < tensor_rank; d++) total *= tensor_shape[d];
+    if (region->offset[0] > total || region->shape[0] > total - region->offset[0])
+      return fail(PH_ERR_INVALID, "region [%llu, +%llu) exceeds the tensor's %llu elements",
+                  (unsigned long long)region->offset[0], (unsigned long long)region->shape[0], (unsigned long long)total);
     spans->push_back({region->offset[0] * es, region->shape[0] * es});
     return PH_OK;
   }
   if (region->rank == 2) {
     if (tensor_rank != 2) return fail(PH_ERR_INVALID, "rank-2 region needs a rank-2 tensor");
+    for (int d = 0; d < 2; d++)
+      if (region->offset[d] > tensor_shape[d] || region->shape[d] > tensor_shape[d] - region->offset[d])
+        return fail(PH_ERR_INVALID, "region axis %d: [%llu, +%llu) exceeds the tensor extent %llu", d,
+                    (unsigned long long)region->offset[d], (unsigned long long)region->shape[d],
+                    (unsigned long long)tensor_shape[d]);
     const uint64_t pitch = tensor_shape[1];
     for (uint64_t r = 0; r < region->shape[0]; r++)
       spans->push_back({((region->offset[0] + r) * pitch + region->offset[1]) * es, region->shape[1] * es});

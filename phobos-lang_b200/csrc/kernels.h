@@ -31,12 +31,14 @@ cudaError_t launch_with_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
 
 // gemm_tc.cu — f16 operands on tcgen05 tensor cores.
 int launch_gemm_tc(const void* A, long long lda, const void* B, long long ldb, void* C, long long ldc, int M, int N,
-                   int K, float alpha, float beta, bool acc_f16, bool c_f16, int bn_override, int sm_count,
+                   int K, float alpha, float beta, bool acc_f16, bool c_f16, int sm_count,
                    uint32_t* status, cudaStream_t stream, const char** err);
-// gemm_tc2.cu — the same operator on CTA pairs (cta_group::2), for large problems.
+// gemm_tc2.cu — the same operator on CTA pairs (cta_group::2), for large problems.  `workspace` (optional,
+// gemm_tc_pair_workspace_bytes, 256-byte aligned) lets the kernel share out its last rounds of tiles by k-blocks.
 int launch_gemm_tc_pair(const void* A, long long lda, const void* B, long long ldb, void* C, long long ldc, int M, int N,
-                        int K, float alpha, float beta, bool acc_f16, bool c_f16, int bn_override, int sm_count,
-                        uint32_t* status, cudaStream_t stream, const char** err);
+                        int K, float alpha, float beta, bool acc_f16, bool c_f16, int sm_count, void* workspace,
+                        size_t workspace_bytes, uint32_t* status, cudaStream_t stream, const char** err);
+size_t gemm_tc_pair_workspace_bytes(int M, int N, int K, int sm_count);
 
 // tmap.cu — TMA descriptors (cuTensorMapEncodeTiled through the runtime's driver entry point).
 enum TmapType { TMAP_F16 = 0, TMAP_F32 = 1 };
@@ -61,7 +63,8 @@ int launch_flash_f16(const void* Q, const void* K, const void* V, void* O, int o
                      int Nq, int Nk, int D, float scale, int sm_count, uint32_t* status, cudaStream_t stream,
                      const char** err);
 
-int set_flash_trace(unsigned long long* device_buf, unsigned long long words);
+// selftest.cu — one CTA whose barrier wait must run out after limit_ns (bounded-wait self-test).
+int launch_selftest_wait(unsigned long long limit_ns, uint32_t* status, cudaStream_t stream, const char** err);
 
 // elementwise.cu — generator and conversions.
 int launch_fill_random(void* out, int dtype_is_f16, unsigned long long n, unsigned long long seed,

@@ -54,8 +54,9 @@ extern "C" int phobos_gemm_fp16tc_noalloc(const PhTensor* A, const PhTensor* B, 
     return ph::fail(PH_ERR_INVALID, "phobos_gemm_fp16tc_noalloc takes f32-stored A, B and C");
   if (A->rank != 2 || B->rank != 2) return ph::fail(PH_ERR_INVALID, "A and B must have rank 2");
   const int64_t M = A->sizes[0], K = A->sizes[1], N = B->sizes[1];
-  const size_t need = phobos_gemm_workspace_bytes(PH_GEMM_FP16TC_FP32ACC, PH_F32, M, N, K);
-  if (M <= 0 || N <= 0 || K <= 0 || need > static_cast<size_t>(PH_NOALLOC_SCRATCH_BYTES))
+  if (M <= 0 || N <= 0 || K <= 0) return ph::fail(PH_ERR_INVALID, "A is %lldx%lld, B has %lld columns", (long long)M, (long long)K, (long long)N);
+  const size_t need = ph::gemm_staging_bytes(M, N, K);
+  if (need > static_cast<size_t>(PH_NOALLOC_SCRATCH_BYTES))
     return ph::fail(PH_ERR_WORKSPACE,
                     "phobos_gemm_fp16tc_noalloc: M=%lld N=%lld K=%lld needs %zu scratch bytes, the built-in scratch holds %d "
                     "(2*(M*K + K*N) bytes must fit); use phobos_gemm with a caller workspace for larger problems",

@@ -118,6 +118,24 @@ def test_executor_reports_arena_exhaustion_and_bad_programs(ph, dev):
             ex.run()
 
 
+def test_store_region_must_match_the_tile(ph, dev, tmp_path):
+    """A STORE whose region holds more elements than the tile is refused (the reference:
+    "store data/region length mismatch", phobos-cluster/src/storage.rs store_f32) and the file stays as it was."""
+    I, tid = ph.Instr, ph.tile_id
+    uri = f"file://{tmp_path}/c.tensor"
+    ph.store_region(uri, (64, 64), (0, 0), np.ones((64, 64), dtype=np.float32))
+    before = (tmp_path / "c.tensor").read_bytes()
+    with ph.Executor(0, 0, 1 << 20) as ex:
+        ex.set_tensors([(uri, ph.F32, (64, 64), ph.RMW)])
+        ex.issue([I(iid=1, op=ph.OP_ALLOC, tile=tid(0, 0, 0), shape=(16, 16), data_type=ph.F32),
+                  I(iid=2, op=ph.OP_LOAD, tile=tid(0, 0, 0), tensor=0, region_offset=(0, 0), region_shape=(16, 16), deps=(1,)),
+                  I(iid=3, op=ph.OP_STORE, tile=tid(0, 0, 0), tensor=0, region_offset=(0, 0), region_shape=(32, 32), deps=(2,))])
+        with pytest.raises(ph.PhobosError) as e:
+            ex.run()
+        assert e.value.code == ph.PH_ERR_STATE and "STORE region" in e.value.message
+    assert (tmp_path / "c.tensor").read_bytes() == before
+
+
 def test_f16_job_through_the_executor(ph, oracle, dev, tmp_path):
     """f16 tiles end to end (the reference's tile store sizes everything as f32, tile_store.rs:110-113)."""
     I, tid = ph.Instr, ph.tile_id

@@ -199,33 +199,65 @@ def test_rejects_bad_descriptors(ph, dev):
     assert e.value.code == ph.PH_ERR_UNSUPPORTED
 
 
-def test_gemm_fp16tc_split_k_tail(ph, oracle, dev, monkeypatch):
-    """The optional split-K tail (last round of tiles cut into K ranges that add into C in turn)."""
+def _workspace(ph, dev, kind, a_dtype, M, N, K):
     import torch
-    monkeypatch.setenv("PHOBOS_GEMM_SPLITK", "1")
-    M, N, K = 4864, 1024, 1024          # 76 pair tiles on 74 pairs: 2 tiles left over -> 4 K ranges each
-    a, b, c = _inputs(oracle, M, N, K)
-    a16, b16 = oracle.fp16_round(a), oracle.fp16_round(b)
-    rows = np.unique(np.concatenate([np.arange(0, M, 97, dtype=np.uint64), np.arange(M - 512, M, 5, dtype=np.uint64)]))
-    want = oracle.gemm_rows(a16, b16, c, 0.5, 1.5, rows=rows)
-    A, B, C = _to(dev, a16, True), _to(dev, b16, True), _to(dev, c)
-    ph.gemm(A, B, C, 0.5, 1.5, ph.GEMM_FP16TC_FP32ACC)
-    assert ph.device_status() == 0
-    assert oracle.rel_frobenius(C.cpu().numpy()[rows.astype(int)], want) <= TOL_F16TC
+    n = ph.gemm_workspace_bytes(kind, a_dtype, M, N, K)
+    return torch.empty((max(n, 256),), dtype=torch.uint8, device=dev), n
 
 
-def test_gemm_fp16tc_two_tiles_in_flight(ph, oracle, dev, monkeypatch):
-    """The optional second tile stream of the pair kernel (own producer, issuer and accumulator)."""
-    monkeypatch.setenv("PHOBOS_GEMM_STREAMS", "2")
-    M, N, K = 4864, 1280, 768           # 95 pair tiles on 74 pairs: pairs with one and with two tiles, ragged K ring
+@pytest.mark.parametrize("shape", [(4864, 1024, 1024), (4864, 1280, 768), (4096, 4096, 1024), (5120, 2304, 520)])
+def test_gemm_fp16tc_stream_k_tail(ph, oracle, dev, shape):
+    """With a workspace the pair kernel shares out its last rounds of tiles by k-blocks: tiles computed by two CTA
+    pairs (one dumps a partial, the other adds it and runs the epilogue) against tiles computed whole, for tile
+    counts just above one round (76, 95), several rounds (256) and a ragged K (520 = 8 k-blocks + 8)."""
+    import torch
+    M, N, K = shape
     a, b, c = _inputs(oracle, M, N, K)
     a16, b16 = oracle.fp16_round(a), oracle.fp16_round(b)
-    rows = np.unique(np.concatenate([np.arange(0, M, 61, dtype=np.uint64), np.arange(M - 256, M, 3, dtype=np.uint64)]))
+    rows = np.unique(np.concatenate([np.arange(0, M, 61, dtype=np.uint64), np.arange(M - 512, M, 3, dtype=np.uint64)]))
     want = oracle.gemm_rows(a16, b16, c, 0.5, 1.5, rows=rows)
-    A, B, C = _to(dev, a16, True), _to(dev, b16, True), _to(dev, c)
-    ph.gemm(A, B, C, 0.5, 1.5, ph.GEMM_FP16TC_FP32ACC)
+    A, B = _to(dev, a16, True), _to(dev, b16, True)
+    ws, need = _workspace(ph, dev, ph.GEMM_FP16TC_FP32ACC, ph.F16, M, N, K)
+    assert need > 0, "this shape must qualify for the stream-K tail"
+    results = []
+    for use_ws in (True, False, True):       # the third call reuses the workspace (stale partials and flags)
+        C = _to(dev, c)
+        ph.gemm(A, B, C, 0.5, 1.5, ph.GEMM_FP16TC_FP32ACC, workspace=ws if use_ws else None)
+        assert ph.device_status() == 0
+        got = C.cpu().numpy()
+        assert oracle.rel_frobenius(got[rows.astype(int)], want) <= TOL_F16TC
+        results.append(got)
+    assert np.array_equal(results[0], results[2]), "a relaunch over a used workspace must give the same bits"
+    # with and without the workspace only the summation order of split tiles differs
+    assert oracle.rel_frobenius(results[0], results[1].astype(np.float64)) <= 1e-5
+    # the f16-accumulate kernel shares the scheduler
+    ch = oracle.fp16_round(c)
+    want16 = oracle.gemm_rows(a16, b16, ch, 1.0, 1.0, rows=rows)
+    ws16, need16 = _workspace(ph, dev, ph.GEMM_FP16, ph.F16, M, N, K)
+    assert need16 > 0
+    Ch = _to(dev, ch, True)
+    ph.gemm(A, B, Ch, 1.0, 1.0, ph.GEMM_FP16, workspace=ws16)
     assert ph.device_status() == 0
-    assert oracle.rel_frobenius(C.cpu().numpy()[rows.astype(int)], want) <= TOL_F16TC
+    assert oracle.rel_frobenius(Ch.float().cpu().numpy()[rows.astype(int)], want16) <= TOL_F16
+
+
+def test_gemm_fp16tc_f32_storage_with_stream_k(ph, oracle, dev):
+    """f32-stored operands: the workspace holds the rounded copies first and the kernel's partial tiles after them;
+    a workspace that only fits the copies still works (tiles computed whole)."""
+    import torch
+    M, N, K = 4864, 1024, 512
+    a, b, c = _inputs(oracle, M, N, K)
+    want = oracle.gemm_rows(oracle.fp16_round(a), oracle.fp16_round(b), c, 1.0, 0.0)
+    A, B = _to(dev, a), _to(dev, b)
+    full = ph.gemm_workspace_bytes(ph.GEMM_FP16TC_FP32ACC, ph.F32, M, N, K)
+    staging = 2 * (M * K + K * N)
+    assert full > staging
+    for nbytes in (full, staging):
+        ws = torch.empty((nbytes,), dtype=torch.uint8, device=dev)
+        C = _to(dev, c)
+        ph.gemm(A, B, C, 1.0, 0.0, ph.GEMM_FP16TC_FP32ACC, workspace=ws)
+        assert ph.device_status() == 0
+        assert oracle.rel_frobenius(C.cpu().numpy(), want) <= TOL_F16TC
 
 
 def test_host_pipeline_matches_direct_calls(ph, oracle, dev):
@@ -268,23 +300,3 @@ def test_saxpy_bit_exact(ph, oracle, dev, n):
         assert not np.array_equal(fused, want)
     with pytest.raises(ph.PhobosError):
         ph.saxpy(X, Y[: n - 4] if n > 4 else Y.reshape(2, 2), O, 1.0)
-
-
-@pytest.mark.parametrize("nsplit", ["1", "0"])
-def test_gemm_fp16tc_split_n_tail(ph, oracle, dev, monkeypatch, nsplit):
-    """The last, partly filled round of 256-wide tiles computed as 128-wide halves (default) or not."""
-    monkeypatch.setenv("PHOBOS_GEMM_NSPLIT", nsplit)
-    M, N, K = 4864, 1024, 512           # 76 pair tiles on 74 pairs: 2 tiles left over -> 4 half tiles
-    a, b, c = _inputs(oracle, M, N, K)
-    a16, b16 = oracle.fp16_round(a), oracle.fp16_round(b)
-    rows = np.unique(np.concatenate([np.arange(0, M, 89, dtype=np.uint64), np.arange(M - 512, M, 3, dtype=np.uint64)]))
-    want = oracle.gemm_rows(a16, b16, c, 0.5, 1.5, rows=rows)
-    A, B, C = _to(dev, a16, True), _to(dev, b16, True), _to(dev, c)
-    ph.gemm(A, B, C, 0.5, 1.5, ph.GEMM_FP16TC_FP32ACC)
-    assert ph.device_status() == 0
-    assert oracle.rel_frobenius(C.cpu().numpy()[rows.astype(int)], want) <= TOL_F16TC
-    # the f16-accumulate kernel shares the scheduler
-    Ch = _to(dev, oracle.fp16_round(c), True)
-    ph.gemm(A, B, Ch, 1.0, 1.0, ph.GEMM_FP16)
-    want16 = oracle.gemm_rows(a16, b16, oracle.fp16_round(c), 1.0, 1.0, rows=rows)
-    assert oracle.rel_frobenius(Ch.float().cpu().numpy()[rows.astype(int)], want16) <= TOL_F16

@@ -76,6 +76,19 @@ def test_storage_region_load_store(ph, tmp_path):
     with pytest.raises(ph.PhobosError) as e:
         ph.load_region(f"file://{tmp_path}/missing", (4, 4), (0, 0), (2, 2))
     assert e.value.code == ph.PH_ERR_IO
+    # a region wider than the tensor would wrap into the next row; one past the last row would read
+    # beyond the file: both are refused before any byte moves
+    before = (tmp_path / "t.tensor").read_bytes()
+    for off, shape in (((0, 6), (2, 6)), ((11, 0), (2, 4)), ((0, 11), (1, 1)), ((13, 0), (1, 1))):
+        with pytest.raises(ph.PhobosError) as e:
+            ph.load_region(uri, (12, 10), off, shape)
+        assert e.value.code == ph.PH_ERR_INVALID and "exceeds" in e.value.message
+        with pytest.raises(ph.PhobosError) as e:
+            ph.store_region(uri, (12, 10), off, np.zeros(shape, dtype=np.float32))
+        assert e.value.code == ph.PH_ERR_INVALID
+    with pytest.raises(ph.PhobosError):
+        ph.load_region(uri, (120,), (118,), (5,))
+    assert (tmp_path / "t.tensor").read_bytes() == before
 
 
 JOB = """\

@@ -73,3 +73,30 @@ def test_noalloc_rejects_what_does_not_fit(ph, dev):
     with pytest.raises(ph.PhobosError) as e:
         ph.gemm_fp16tc_noalloc(H, H, torch.zeros((256, 256), device=dev), 1.0, 0.0)
     assert e.value.code == ph.PH_ERR_INVALID
+
+
+def test_noalloc_validates_before_it_touches_the_scratch(ph, dev):
+    """K = 132 is a legal f32 row length (a multiple of 4) but not a legal f16 one (not a multiple of 8):
+    the call must be refused before any staging kernel is queued, leaving C as it was."""
+    import torch
+    A, B, C = _problem(ph, dev, 256, 256, 132, 41)
+    keep = C.clone()
+    with pytest.raises(ph.PhobosError) as e:
+        ph.gemm_fp16tc_noalloc(A, B, C, 1.0, 0.0)
+    assert e.value.code == ph.PH_ERR_INVALID
+    torch.cuda.synchronize()
+    assert torch.equal(C, keep)
+
+
+def test_noalloc_uses_the_last_byte_of_the_scratch(ph, oracle, dev):
+    """2*(M*K + K*N) equal to the scratch size exactly."""
+    import torch
+    M, N, K = 2048, 2048, 1024
+    assert 2 * (M * K + K * N) == ph.NOALLOC_SCRATCH_BYTES
+    A, B, C = _problem(ph, dev, M, N, K, 51)
+    c0 = C.cpu().numpy()
+    ph.gemm_fp16tc_noalloc(A, B, C, 1.0, 1.0)
+    assert ph.device_status() == 0
+    rows = np.array([0, 1, 777, M - 1], dtype=np.uint64)
+    want = oracle.gemm_rows(A.cpu().numpy(), B.cpu().numpy(), c0, 1.0, 1.0, rows=rows, round_inputs_f16=True)
+    assert oracle.rel_frobenius(C.cpu().numpy()[rows.astype(int)], want) <= 2e-3
