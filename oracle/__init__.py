@@ -45,6 +45,8 @@ def lib() -> ctypes.CDLL:
         L.ph_oracle_lcg_next_u64.argtypes = [_u64p]
         L.ph_oracle_lcg_fill.argtypes = [ctypes.c_uint64, ctypes.c_uint64, ctypes.c_float, _f32p]
         L.ph_oracle_lcg_fill_normal.argtypes = [ctypes.c_uint64, ctypes.c_uint64, _f32p]
+        L.ph_oracle_lcg_fill_normal_at.argtypes = [ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64, _f32p]
+        L.ph_oracle_lcg_fill_block.argtypes = [ctypes.c_uint64] * 5 + [ctypes.c_float, _f32p]
         L.ph_oracle_f32_to_f16_bits.argtypes = [_f32p, ctypes.c_uint64, _u16p]
         L.ph_oracle_f16_bits_to_f32.argtypes = [_u16p, ctypes.c_uint64, _f32p]
         L.ph_oracle_sample_points.argtypes = [ctypes.c_uint64, ctypes.c_uint64, _u64p]
@@ -108,9 +110,18 @@ def lcg_fill(seed: int, n: int, scale: float = 1.0) -> np.ndarray:
     return out
 
 
-def lcg_fill_normal(seed: int, n: int) -> np.ndarray:
+def lcg_fill_block(seed: int, first: int, rows: int, cols: int, pitch: int, scale: float = 1.0) -> np.ndarray:
+    """A [rows, cols] block of a larger seeded tensor: element (r, c) is stream element first + r*pitch + c."""
+    out = np.empty((rows, cols), dtype=np.float32)
+    lib().ph_oracle_lcg_fill_block(seed, first, rows, cols, pitch, scale, _p(out, _f32p))
+    return out
+
+
+def lcg_fill_normal(seed: int, n: int, first: int = 0) -> np.ndarray:
+    """N(0,1) by Box-Muller over the Lcg stream, from element `first` (even) on."""
+    assert first % 2 == 0
     out = np.empty(n, dtype=np.float32)
-    lib().ph_oracle_lcg_fill_normal(seed, n, _p(out, _f32p))
+    lib().ph_oracle_lcg_fill_normal_at(seed, first, n, _p(out, _f32p))
     return out
 
 

@@ -82,11 +82,31 @@ PH_EXPORT void ph_oracle_lcg_fill(uint64_t seed, uint64_t n, float scale, float 
   }
 }
 
+/* Rows [0, rows) x columns [0, cols) of a block of a larger seeded tensor: out[r][c] is
+ * stream element first + r*pitch + c (scaled).  This is how a rank reads its shard of a
+ * tensor that `phobos-tensor init --fill random` wrote as one stream
+ * (phobos-cluster/src/bin/phobos-tensor.rs:55-72, row-major, storage.rs:22-46). */
+PH_EXPORT void ph_oracle_lcg_fill_block(uint64_t seed, uint64_t first, uint64_t rows, uint64_t cols, uint64_t pitch,
+                                        float scale, float *out) {
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < (int64_t)rows; r++) {
+    uint64_t s = lcg_skip(seed, first + (uint64_t)r * pitch);
+    float *o = out + (uint64_t)r * cols;
+    for (uint64_t c = 0; c < cols; c++) o[c] = scale * lcg_unit(&s);
+  }
+}
+
 /* N(0,1) by Box-Muller over consecutive Lcg pairs.  The reference has no
  * normal generator; this exists because the flash_fp16 benchmark config asks
  * for N(0,1) inputs.  u1 = (unit+1)/2 mapped into (0,1], u2 likewise. */
+PH_EXPORT void ph_oracle_lcg_fill_normal_at(uint64_t seed, uint64_t first, uint64_t n, float *out);
 PH_EXPORT void ph_oracle_lcg_fill_normal(uint64_t seed, uint64_t n, float *out) {
+  ph_oracle_lcg_fill_normal_at(seed, 0, n, out);
+}
+/* The same stream from element `first` on (first must be even: elements come in pairs). */
+PH_EXPORT void ph_oracle_lcg_fill_normal_at(uint64_t seed, uint64_t first, uint64_t n, float *out) {
   uint64_t pairs = (n + 1) / 2;
+  seed = lcg_skip(seed, first);
 #pragma omp parallel
   {
 #ifdef _OPENMP

@@ -24,30 +24,36 @@
 //   warp 8     TMA producer: Q once, then K and V blocks of 128 keys through one
 //              ring of five slots (a block takes thousands of clocks to land while
 //              the MMAs saturate shared memory, so the ring runs two blocks ahead)
-//   warp 9     tcgen05.mma issuer (one thread) for both tiles, in a fixed order per
-//              key block j: O_0 += P_0(j) V_j, S_0 = Q_0 K_{j+1}^T, O_1 += P_1(j) V_j,
-//              S_1 = Q_1 K_{j+1}^T.  The fixed order is what keeps the two tiles half
-//              a period apart (two free-running issuers fall into lockstep, and then
-//              both tiles' exponentials compete for the MUFU unit at the same time).
-//   warps 10,11 idle (complete the third warpgroup)
-// Tensor memory columns: S0 | S1 | O0 | O1.  P_i (f16) overwrites the low half of
-// S_i and is the A operand of O_i += P_i V straight from tensor memory.
-//
-// Hand-over of P in slices: a softmax thread holds its whole row of S in registers,
-// and writes P back in P_SLICES slices of 128 / P_SLICES keys, each with its own
-// mbarrier.  The issuer starts the MMAs of a slice as soon as that slice is there, so
-// all but the last slice's share of O += P V runs while the softmax warps are still
-// busy with later exponentials; only the last slice and the next S = Q K^T remain on
-// the dependency chain S(j) -> P(j) -> S(j+1) of a tile.
+//   warps 9,10 tcgen05.mma issuers, one per query tile: S_i = Q_i K^T into tensor
+//              memory, then O_i += P_i V with P_i read from tensor memory (it
+//              overwrites S_i).  They take strict turns, so the two tiles keep
+//              ping-ponging, but each issuer does the barrier waits of its next
+//              batch while the other one issues (a tcgen05.mma blocks its thread
+//              until the pipe accepts it; two free-running issuers fell into
+//              lockstep and were 20% slower)
+//   warp 11    idle (completes the third warpgroup)
+// Tensor memory columns: S0 | S1 | O0 | O1.
 //
 // Exponentials: a 128x128 score tile needs 16384 exp2; the MUFU unit delivers 16
 // per clock per SM, i.e. 1024 clocks per tile, the same order as the tensor core's
 // time for the tile's two MMAs, so the two units have to overlap: that is what the
 // two-tile ping-pong is for.  The scale/subtract and the row sums use packed f32x2
 // instructions to halve their issue slots.
+//
+// Measured and not adopted (B4 H32 S4096 D128, this structure at 1108 TFLOP/s):
+//  * P handed over in slices, each with its own barrier, so that O += P V could start
+//    before the block's softmax has finished, with one issuing thread for both tiles:
+//    1043 / 1015 / 867 / 639 TFLOP/s for 1 / 2 / 4 / 8 slices; each hand-over costs a
+//    tcgen05.wait::st of some hundred clocks in the softmax warps;
+//  * the first half of P stored to tensor memory while the second half is computed
+//    (1099), S fetched in two halves with the maximum of the first taken while the
+//    second is on its way (1106), both (1089);
+//  * one or two of every eight exponential pairs as a cubic on the FMA pipes
+//    (2^x = 2^n p(f), relative error 7.5e-5, well inside f16): 1085 / 1074.
+// The loop is bound by the dependency chain of a tile, softmax(j) -> P -> O += P V and
+// S(j+1) -> softmax(j+1) (S, P and O of both tiles fill the 512 tensor-memory columns
+// at D = 128, so S cannot be double buffered), not by a pipe.
 #include <cuda.h>
-
-#include <cstdlib>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -58,11 +64,6 @@ namespace {
 constexpr int QT = 128;        // query rows per tile
 constexpr int KB = 128;        // keys per block
 constexpr int FL_THREADS = 384;
-#ifndef PH_FLASH_P_SLICES
-#define PH_FLASH_P_SLICES 4
-#endif
-constexpr int P_SLICES = PH_FLASH_P_SLICES;   // hand-over pieces of a P block (1, 2, 4 or 8)
-constexpr int SLICE_KEYS = KB / P_SLICES;     // keys per piece: 16, 32, 64 or 128
 constexpr float RESCALE_TAU = 8.0f;          // log2 units
 constexpr float M_INIT = -65504.0f * 1.4426950408889634f;  // the .ph's -65504 in log2 units
 
@@ -73,7 +74,7 @@ struct FCfg {
   static constexpr int KV_BYTES = KB * D * 2;
   static constexpr int HALF_BYTES = 128 * 128;        // one [128 rows x 64 f16] box
   static constexpr int RING = 5;                      // K/V blocks in flight (shared ring)
-  static constexpr int SMEM_BYTES = 2 * QTILE_BYTES + RING * KV_BYTES + 1024 + 512;
+  static constexpr int SMEM_BYTES = 2 * QTILE_BYTES + RING * KV_BYTES + 1024 + 256;
   static constexpr int TMEM_COLS = 512;
   static constexpr int S_COL0 = 0;                    // S_i at i*128
   static constexpr int O_COL0 = 256;                  // O_i at 256 + i*D
@@ -99,34 +100,6 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
   return r;
 }
 
-// N consecutive 32-bit tensor-memory columns of this thread's lane, from registers.
-template <int N>
-__device__ __forceinline__ void tmem_st_slice(uint32_t taddr, const uint32_t (&r)[N]) {
-  static_assert(N == 8 || N == 16 || N == 32 || N == 64, "slice width");
-  if constexpr (N == 8) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(r[0]),
-                 "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
-                 : "memory");
-  } else if constexpr (N == 16) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
-        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
-        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-        : "memory");
-  } else if constexpr (N == 32) {
-    tmem_st_32x32b_x32(taddr, r);
-  } else {
-    uint32_t lo[32], hi[32];
-#pragma unroll
-    for (int e = 0; e < 32; e++) {
-      lo[e] = r[e];
-      hi[e] = r[32 + e];
-    }
-    tmem_st_32x32b_x32(taddr, lo);
-    tmem_st_32x32b_x32(taddr + 32, hi);
-  }
-}
 __device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
   float2 d;
   asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
@@ -165,33 +138,35 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* kv_full = bars + 1;            // RING
   uint64_t* kv_empty = bars + 1 + RING;    // RING
   uint64_t* s_full = bars + 1 + 2 * RING;  // 2 (per query tile)
-  uint64_t* o_done = s_full + 2;           // 2
-  uint64_t* p_full = s_full + 4;           // 2 x P_SLICES: [tile][slice]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(p_full + 2 * P_SLICES);
+  uint64_t* p_full = s_full + 2;           // 2
+  uint64_t* o_done = s_full + 4;           // 2
+  uint64_t* turn = s_full + 6;             // 2 (issuer hand-off)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 8);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const WaitCtx wctx{abort_flag, p.status};
+  // one CTA in the middle of the grid reports the SM clock it saw
+  __shared__ unsigned long long clock_slot[2];
+  const bool clock_cta = threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == (gridDim.y >> 1);
+  if (clock_cta) launch_clock_begin(clock_slot);
   const int head = blockIdx.y;
   const int q_row0 = blockIdx.x * (2 * QT);
   const int nkb = p.n_kblocks;
-  // one CTA in the middle of the grid reports the SM clock it saw
-  const bool clock_cta = threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == (gridDim.y >> 1);
-  __shared__ unsigned long long clock_slot[2];
-  if (clock_cta) launch_clock_begin(clock_slot);
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < RING; s++) {
       mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
+      mbar_init(&kv_empty[s], 2);  // released by both issuers
     }
     for (int s = 0; s < 2; s++) {
       mbar_init(&s_full[s], 1);
+      mbar_init(&p_full[s], 4);    // one arrival per softmax warp
       mbar_init(&o_done[s], 1);
+      mbar_init(&turn[s], 1);
     }
-    for (int s = 0; s < 2 * P_SLICES; s++) mbar_init(&p_full[s], 4);  // one arrival per softmax warp
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tmQ);
@@ -209,7 +184,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
   if (warp >= 8) {
   // the third warpgroup hands registers to the softmax warpgroups
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 120;");
   if (warp == 8) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
@@ -233,8 +208,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       }
     }
-  } else if (warp == 9) {
-    // ------------------------------ MMA issuer (both tiles) ---------------------------
+  } else if (warp <= 10) {
+    // ------------------------------ MMA issuers (warp 9: tile 0, warp 10: tile 1) ---
     if (lane == 0) {
       // S = Q K^T : M=128 (queries), N=128 (keys), both operands K-major
       const uint32_t idesc_s = umma_idesc_f16(QT, KB, true, false, false) | (p.negate_q ? (1u << 13) : 0u);
@@ -255,14 +230,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           umma_f16_ss(d, qd + off, kd + off, idesc_s, kk != 0 ? 1u : 0u);
         }
       };
-      // the MMAs of P slice `sl` (keys sl*SLICE_KEYS ...): 16 keys each
-      auto issue_pv_slice = [&](int i, int slot, int sl, bool accumulate) {
+      auto issue_pv = [&](int i, int slot, bool accumulate) {
         const uint64_t vd = v_desc0 + static_cast<uint64_t>(slot * (C_::KV_BYTES >> 4));
         const uint32_t d = tmem_base + C_::O_COL0 + i * D;
         const uint32_t pa = tmem_base + C_::S_COL0 + i * 128;  // P overwrote S, 2 f16 per column
 #pragma unroll
-        for (int k2 = 0; k2 < SLICE_KEYS / 16; k2++) {
-          const int kk = sl * (SLICE_KEYS / 16) + k2;
+        for (int kk = 0; kk < KB / 16; kk++) {
           // V block: [128 keys][64 d] per half; 8-key atoms 1024 B apart, halves HALF_BYTES apart;
           // a step of 16 keys is 2048 B
           umma_f16_ts(d, pa + kk * 8, vd + static_cast<uint64_t>(kk * (2048 >> 4)), idesc_o,
@@ -278,13 +251,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           cpar ^= 1;
         }
       };
+      // Issuer warp 9 owns query tile 0, warp 10 tile 1.  They take turns: while
+      // one issues its 16 MMAs (each tcgen05.mma blocks its thread until the pipe
+      // accepts it, ~96 clocks), the other performs the barrier waits of its next
+      // batch, so the tensor pipe never idles behind a wait.  turn[t] is arrived by
+      // the other issuer when its batch is issued.
+      const int i = warp - 9;
       bool ok = mbar_wait(q_full, 0, SITE_FLASH_MMA, wctx) && mbar_wait(&kv_full[cur], cpar, SITE_FLASH_MMA, wctx);
       if (ok) {
         tc_fence_after_sync();
-        issue_s(0, cur);
-        umma_commit(&s_full[0]);
-        issue_s(1, cur);
-        umma_commit(&s_full[1]);
+        issue_s(i, cur);
+        umma_commit(&s_full[i]);
         umma_commit(&kv_empty[cur]);
         advance();
       }
@@ -298,33 +275,27 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           if (!mbar_wait(&kv_full[ks], cpar, SITE_FLASH_MMA, wctx)) break;
           advance();
         }
-#pragma unroll
-        for (int i = 0; i < 2 && ok; i++) {
-#pragma unroll
-          for (int sl = 0; sl < P_SLICES; sl++) {
-            if (!mbar_wait(&p_full[i * P_SLICES + sl], j & 1, SITE_FLASH_MMA, wctx)) {
-              ok = false;
-              break;
-            }
-            tc_fence_after_sync();
-            issue_pv_slice(i, vs, sl, j > 0);
-          }
-          if (!ok) break;
-          if (i == 1) umma_commit(&kv_empty[vs]);
-          if (more) {
-            issue_s(i, ks);
-            umma_commit(&s_full[i]);
-            if (i == 1) umma_commit(&kv_empty[ks]);
-          } else {
-            umma_commit(&o_done[i]);
-          }
+        // my turn: tile 0 goes first in every round (its barrier passes once before any arrival)
+        if (!mbar_wait(&turn[i], i == 0 ? ((j & 1) ^ 1) : (j & 1), SITE_FLASH_MMA, wctx)) break;
+        // P_i is the late input: everything else has been waited for by now
+        if (!mbar_wait(&p_full[i], j & 1, SITE_FLASH_MMA, wctx)) break;
+        tc_fence_after_sync();
+        issue_pv(i, vs, j > 0);
+        umma_commit(&kv_empty[vs]);
+        if (more) {
+          issue_s(i, ks);
+          umma_commit(&s_full[i]);
+          umma_commit(&kv_empty[ks]);
+        } else {
+          umma_commit(&o_done[i]);
         }
+        mbar_arrive(&turn[i ^ 1]);
       }
     }
   }
   } else {
     // ------------------------------ softmax / correction / epilogue ---------------
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 192;");
     const int i = warp >> 2;       // query tile
     const int q = warp & 3;        // TMEM lane quarter
     const int row_in_tile = q * 32 + lane;
@@ -335,7 +306,6 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const float c = p.scale_log2;
     float m2 = M_INIT, l = 0.0f;
     bool ok = true;
-
     for (int j = 0; j < nkb; j++) {
       // the vote keeps the warp together: the TMEM loads below are warp-collective
       if (!PH_WARP_WAIT(&s_full[i], j & 1, SITE_FLASH_SOFTMAX, wctx)) {
@@ -344,10 +314,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       tc_fence_after_sync();
       uint32_t sr[4][32];
+      const int valid = p.Nk - j * KB;  // keys of this block that exist
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
       for (int cc = 0; cc < 4; cc++) tmem_ld_32x32b_x32(s_addr + cc * 32, sr[cc]);
       tmem_ld_wait();
-      const int valid = p.Nk - j * KB;  // keys of this block that exist
       if (valid < KB) {
 #pragma unroll
         for (int cc = 0; cc < 4; cc++)
@@ -355,7 +326,6 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           for (int e = 0; e < 32; e++)
             if (cc * 32 + e >= valid) sr[cc][e] = 0xFF800000u;  // -inf
       }
-      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
       for (int e = 0; e < 32; e += 2) {
         mx0 = max3(mx0, __uint_as_float(sr[0][e]), __uint_as_float(sr[0][e + 1]));
@@ -387,34 +357,32 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       }
       const float2 c2 = make_float2(c, c), neg_m2 = make_float2(-m2, -m2);
+      uint32_t pk[2][32];
       float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
 #pragma unroll
-      for (int sl = 0; sl < P_SLICES; sl++) {
-        constexpr int SLICE_REGS = SLICE_KEYS / 2;   // f16 pairs per slice
-        uint32_t pk[SLICE_REGS];
+      for (int cc = 0; cc < 4; cc++) {
 #pragma unroll
-        for (int e = 0; e < SLICE_KEYS; e += 2) {
-          const int col = sl * SLICE_KEYS + e;      // column inside the key block
-          const int cc = col >> 5, ce = col & 31;
-          const float2 x = ffma2(make_float2(__uint_as_float(sr[cc][ce]), __uint_as_float(sr[cc][ce + 1])), c2, neg_m2);
+        for (int e = 0; e < 32; e += 2) {
+          const float2 x = ffma2(make_float2(__uint_as_float(sr[cc][e]), __uint_as_float(sr[cc][e + 1])), c2, neg_m2);
           float2 pr;
           pr.x = ex2_approx(x.x);
           pr.y = ex2_approx(x.y);
           if (valid < KB) {  // keys past the end contribute nothing
-            if (col >= valid) pr.x = 0.0f;
-            if (col + 1 >= valid) pr.y = 0.0f;
+            if (cc * 32 + e >= valid) pr.x = 0.0f;
+            if (cc * 32 + e + 1 >= valid) pr.y = 0.0f;
           }
           if ((e & 2) == 0) la = fadd2(la, pr);
           else lb = fadd2(lb, pr);
-          pk[e >> 1] = pack_f16x2(pr.x, pr.y);
+          pk[cc >> 1][(cc & 1) * 16 + (e >> 1)] = pack_f16x2(pr.x, pr.y);
         }
-        tmem_st_slice<SLICE_REGS>(s_addr + sl * SLICE_REGS, pk);
-        tmem_st_wait();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&p_full[i * P_SLICES + sl]);
       }
       l += (la.x + la.y) + (lb.x + lb.y);
+      tmem_st_32x32b_x32(s_addr, pk[0]);
+      tmem_st_32x32b_x32(s_addr + 32, pk[1]);
+      tmem_st_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[i]);
     }
 
     if (ok && PH_WARP_WAIT(&o_done[i], 0, SITE_FLASH_EPI, wctx)) {

@@ -12,8 +12,8 @@
 // the mbarriers of both CTAs.  No TMA multicast is used: every CTA loads its
 // own operand slices.
 //
-// Warp roles per CTA (192 threads): warp 0 TMA producer, warp 1 MMA issuer
-// (leader CTA only) and tensor-memory owner, warps 2..5 epilogue
+// Warp roles per CTA (320 threads): warp 0 TMA producer, warp 1 MMA issuer
+// (leader CTA only) and tensor-memory owner, warps 2..9 epilogue
 // (tcgen05.ld -> alpha*acc + beta*C_old -> global).  Two accumulator buffers of
 // 256 columns let the epilogue of one work item overlap the main loop of the next.
 // BN is a run-time multiple of 16 (<= 256): 256 unless N is narrower.
@@ -24,8 +24,13 @@
 // band, so that the A rows of a band and the B panels at the turn stay in L2.
 // When the tile count is not a multiple of P the last round would leave pairs
 // idle (4096^3: 256 tiles on 74 pairs = 3.46 rounds).  With a workspace from the
-// caller, the last full round and the remainder are therefore cut stream-K
-// style: their k-blocks, laid end to end, are split into P equal ranges.  A range
+// caller, the last full round and the remainder are therefore shared out stream-K
+// style: each of these tiles is cut along K into g equal pieces, and the pieces, laid
+// end to end, are dealt to the P pairs as evenly as whole pieces go (4096^3: halves,
+// three per pair, 1.5 tiles instead of 2).  Pieces are never shorter than 24 k-blocks:
+// an epilogue takes about as long as 27 k-blocks of MMAs and there are two accumulator
+// buffers, so shorter items would make the MMA issuer wait for the epilogue warps
+// (measured: 107 us with ranges cut anywhere, against 104 us without sharing).  A range
 // is at least one tile long, so a tile is shared by at most two pairs: the pair
 // whose range ENDS inside the tile computes its first k-blocks (as the last item
 // of its list) and the pair whose range STARTS inside it the rest (as the first
@@ -45,20 +50,20 @@ namespace {
 constexpr int BM = 128;       // rows per CTA; 256 per pair
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
-constexpr int NUM_THREADS = 192;
-constexpr int EPI_WARP0 = 2;  // warps 2..5: TMEM lane quarter = warp & 3 -> 2, 3, 0, 1
+constexpr int NUM_THREADS = 320;
+constexpr int EPI_WARP0 = 2;  // warps 2..9: TMEM lane quarter = warp & 3 -> 2, 3, 0, 1, 2, 3, 0, 1
 constexpr int STAGES = 6;
 constexpr int A_BYTES = BM * BK * 2;          // 16 KB
 constexpr int B_BYTES = BK * 128 * 2;         // 16 KB: up to 128 columns (two 64-column boxes) per CTA
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int EPI_LD = 36;                    // floats per row of an epilogue transpose pad (32 + 4: conflict-free)
-constexpr int EPI_BYTES = 4 * 32 * EPI_LD * 4; // one 32 x 32 pad per epilogue warp
+constexpr int EPI_BYTES = 8 * 32 * 32 * 4;    // one swizzled 32 x 32 f32 transpose pad per epilogue warp
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + EPI_BYTES;
 constexpr int TMEM_COLS = 512;
 constexpr int ACC_STRIDE = 256;               // tensor-memory columns per accumulator buffer
-constexpr int SK_MIN_PIECE = 4;               // k-blocks: range boundaries closer than this to a tile edge snap to it
+constexpr int SK_MIN_PIECE = 24;              // k-blocks: no shared tile is cut into pieces shorter than this
 constexpr int SK_SLOT_WORDS = 2 * 4 * 32 * 256;  // one partial tile: [cta][warp][column][lane] 32-bit words
 constexpr int FLAG_BANKS = 8;                 // launches that may be in flight per device
+constexpr int MAX_PAIRS = 128;
 
 enum ItemRole : int { ROLE_FULL = 0, ROLE_DUMP = 1, ROLE_FIXUP = 2 };
 
@@ -74,26 +79,20 @@ struct Tc2Params {
   // stream-K part: tiles [dp_tiles, dp_tiles + sk_tiles) are shared out by k-blocks
   int dp_tiles;
   int sk_tiles;           // 0: every tile is computed whole by one pair
+  int sk_g;               // pieces per shared tile
+  // Start of every pair's range of the shared tiles, in k-blocks from the first shared tile (entry `pairs` is the
+  // end).  The shared tiles are cut into sk_g equal pieces each and the pieces are dealt out as evenly as whole
+  // pieces go, so a range starts and ends on piece boundaries and every item is at least a piece long.  Worked
+  // out on the host: the device would spend a microsecond of 64-bit divisions on it between two items.
+  int sk_bound[MAX_PAIRS + 1];
   uint32_t* partials;     // workspace: slot b (boundary between pair b-1 and pair b) at b * SK_SLOT_WORDS
-  uint32_t* flags;        // [bank][boundary][cta][warp], raised to `epoch` when a partial is complete
+  uint32_t* flags;        // [bank][boundary][cta][quarter][parity], raised to `epoch` when a partial is complete
   uint32_t epoch;
 };
 
 struct Item {
   int tile, kb0, kb1, role, slot;
 };
-
-// Start of pair i's stream-K range, in k-blocks from the first stream-K tile.
-__device__ __forceinline__ long long sk_boundary(const Tc2Params& p, int i, int num_pairs, int num_kb) {
-  const long long total = static_cast<long long>(p.sk_tiles) * num_kb;
-  if (i <= 0) return 0;
-  if (i >= num_pairs) return total;
-  long long b = total * i / num_pairs;
-  const int frac = static_cast<int>(b % num_kb);
-  if (frac < SK_MIN_PIECE) b -= frac;
-  else if (frac > num_kb - SK_MIN_PIECE) b += num_kb - frac;
-  return b;
-}
 
 // Item n of pair `pair`'s list; false when the list has ended.
 __device__ __forceinline__ bool work_item(const Tc2Params& p, int pair, int num_pairs, int num_kb, int n, Item& w) {
@@ -107,13 +106,13 @@ __device__ __forceinline__ bool work_item(const Tc2Params& p, int pair, int num_
     return true;
   }
   if (p.sk_tiles == 0) return false;
-  const long long s = sk_boundary(p, pair, num_pairs, num_kb), e = sk_boundary(p, pair + 1, num_pairs, num_kb);
-  const long long t = s / num_kb + (n - n_dp);
-  const long long ps = max(s, t * num_kb), pe = min(e, (t + 1) * num_kb);
+  const int s = p.sk_bound[pair], e = p.sk_bound[pair + 1];
+  const int t = s / num_kb + (n - n_dp);
+  const int ps = max(s, t * num_kb), pe = min(e, (t + 1) * num_kb);
   if (ps >= pe) return false;
-  w.tile = p.dp_tiles + static_cast<int>(t);
-  w.kb0 = static_cast<int>(ps - t * num_kb);
-  w.kb1 = static_cast<int>(pe - t * num_kb);
+  w.tile = p.dp_tiles + t;
+  w.kb0 = ps - t * num_kb;
+  w.kb1 = pe - t * num_kb;
   if (w.kb0 == 0 && w.kb1 == num_kb) {
     w.role = ROLE_FULL;
     w.slot = 0;
@@ -151,7 +150,8 @@ __device__ __forceinline__ void pair_tile_coords(int t, const Tc2Params& p, int&
 
 template <bool ACC_F16, typename CT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
-gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Tc2Params p) {
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                const __grid_constant__ Tc2Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
@@ -181,7 +181,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
     for (int s = 0; s < 2; s++) {
       mbar_init(&tmem_full[s], 1);
-      mbar_init(&tmem_empty[s], 8);  // four epilogue warps in each CTA of the pair
+      mbar_init(&tmem_empty[s], 16);  // eight epilogue warps in each CTA of the pair
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -275,7 +275,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
   } else {
     // ------------------------------ epilogue (both CTAs) ---------------------------
-    const int q = warp & 3;   // the TMEM lane quarter this warp may read
+    // Eight warps: two per tensor-memory lane quarter (a warp may only read the quarter warp % 4), each taking
+    // every other 32-column chunk of its 32 rows.  The time of an epilogue is a chain of global-memory round
+    // trips (C_old of a chunk must arrive before the chunk can be written), one per chunk: splitting the chunks
+    // over two warps and requesting a warp's next C_old chunk before it works on the current one cut the chain
+    // from eight exposed round trips to about two.
+    const int q = warp & 3;
+    const int half = (warp - EPI_WARP0) >> 2;   // 0: even chunks, 1: odd chunks
     int acc = 0;
     uint32_t acc_phase = 0;
     Item w;
@@ -286,13 +292,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       tc_fence_after_sync();
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * ACC_STRIDE;
       const int chunks = (p.bn + 31) >> 5;
-      // this warp's part of a partial tile: [column][lane], so that a warp instruction moves 128 contiguous bytes
+      // this quarter's part of a partial tile: [column][lane], so that a warp instruction moves 128 contiguous bytes
       uint32_t* part = p.partials + static_cast<size_t>(w.slot) * SK_SLOT_WORDS +
                        static_cast<size_t>((rank * 4 + q) * 256) * 32 + lane;
-      uint32_t* flag = p.flags + (((p.epoch % FLAG_BANKS) * 128 + w.slot) * 2 + rank) * 4 + q;
+      uint32_t* flag = p.flags + ((((p.epoch % FLAG_BANKS) * 128 + w.slot) * 2 + rank) * 4 + q) * 2 + half;
       if (w.role == ROLE_DUMP) {
 #pragma unroll 1
-        for (int c = 0; c < chunks; c++) {
+        for (int c = half; c < chunks; c += 2) {
           uint32_t r[32];
           tmem_ld_32x32b_x32(t_addr + c * 32, r);
           tmem_ld_wait();
@@ -335,45 +341,61 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       CT* crow = reinterpret_cast<CT*>(p.C) + static_cast<long long>(row) * p.ldc;
       const int tile_col0 = nb * p.bn;
       const int col_end = min(p.N, tile_col0 + p.bn);
+      // the other pair's partial of the chunk in hand, requested one chunk ahead of its use
+      uint32_t pcur[32];
+      if (fixup && half < chunks) {
+#pragma unroll
+        for (int v = 0; v < 32; v++) pcur[v] = __ldcg(part + (half * 32 + v) * 32);
+      }
       if constexpr (sizeof(CT) == 4) {
         // f32 C.  The accumulator arrives one row per lane; going to global memory that
         // way makes every warp instruction touch 32 different rows (16 useful bytes per
-        // 32-byte sector, poor DRAM locality: measured 17 us per tile).  Each 32x32 chunk
-        // is therefore transposed through a per-warp shared-memory pad so that a warp
-        // instruction covers 4 rows x 128 contiguous bytes; the C_old values of the
-        // chunk are requested before the transpose so their latency overlaps it.
-        float* pad = epi_pad + q * (32 * EPI_LD);
-        const int sub_row = lane >> 3, sub_col = (lane & 7) * 4;
+        // 32-byte sector, poor DRAM locality).  Each 32x32 chunk is therefore transposed
+        // through a per-warp shared-memory pad (16-byte groups XOR-swizzled by row, so both
+        // directions run at four wavefronts per 512 bytes) and a warp instruction covers
+        // 4 rows x 128 contiguous bytes of C.
+        float* pad = epi_pad + (warp - EPI_WARP0) * (32 * 32);
+        const int sub_row = lane >> 3, grp = lane & 7, sub_col = grp * 4;
         const long long row_base = static_cast<long long>(mb) * (2 * BM) + static_cast<int>(rank) * BM + q * 32;
-#pragma unroll 1
-        for (int c = 0; c < chunks; c++) {
+        auto load_old = [&](int c, float4 (&dst)[8]) {
           const int col = tile_col0 + c * 32 + sub_col;
-          const bool col_ok = col < col_end;
-          float4 old[8];
+          const bool col_ok = c < chunks && col < col_end;
 #pragma unroll
           for (int it = 0; it < 8; it++) {
             const long long rr = row_base + it * 4 + sub_row;
             const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.C) + rr * p.ldc + col);
-            old[it] = (col_ok && rr < p.M) ? *src : make_float4(0.f, 0.f, 0.f, 0.f);
+            dst[it] = (col_ok && rr < p.M) ? *src : make_float4(0.f, 0.f, 0.f, 0.f);
           }
+        };
+        float4 old[8];
+        load_old(half, old);
+#pragma unroll 1
+        for (int c = half; c < chunks; c += 2) {
+          const int col = tile_col0 + c * 32 + sub_col;
+          const bool col_ok = col < col_end;
           uint32_t r[32];
           tmem_ld_32x32b_x32(t_addr + c * 32, r);
           tmem_ld_wait();
           if (fixup) {
 #pragma unroll
-            for (int v = 0; v < 32; v++)
-              r[v] = __float_as_uint(__uint_as_float(r[v]) + __uint_as_float(__ldcg(part + (c * 32 + v) * 32)));
+            for (int v = 0; v < 32; v++) r[v] = __float_as_uint(__uint_as_float(r[v]) + __uint_as_float(pcur[v]));
+            if (c + 2 < chunks) {   // the registers are free again: request this warp's next chunk of the partial
+#pragma unroll
+              for (int v = 0; v < 32; v++) pcur[v] = __ldcg(part + ((c + 2) * 32 + v) * 32);
+            }
           }
           __syncwarp();  // the previous chunk's reads of the pad are done
 #pragma unroll
           for (int v = 0; v < 8; v++)
-            *reinterpret_cast<uint4*>(pad + lane * EPI_LD + v * 4) = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+            *reinterpret_cast<uint4*>(pad + lane * 32 + ((v ^ (lane & 7)) << 2)) =
+                make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
           __syncwarp();
 #pragma unroll
           for (int it = 0; it < 8; it++) {
-            const long long rr = row_base + it * 4 + sub_row;
+            const int pr = it * 4 + sub_row;
+            const long long rr = row_base + pr;
             if (col_ok && rr < p.M) {
-              const float4 a4 = *reinterpret_cast<const float4*>(pad + (it * 4 + sub_row) * EPI_LD + sub_col);
+              const float4 a4 = *reinterpret_cast<const float4*>(pad + pr * 32 + ((grp ^ (pr & 7)) << 2));
               float4 o;
               o.x = __fadd_rn(__fmul_rn(p.alpha, a4.x), __fmul_rn(p.beta, old[it].x));
               o.y = __fadd_rn(__fmul_rn(p.alpha, a4.y), __fmul_rn(p.beta, old[it].y));
@@ -382,10 +404,23 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
               *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.C) + rr * p.ldc + col) = o;
             }
           }
+          load_old(c + 2, old);   // in flight while the next chunk's accumulator is fetched and transposed
         }
       } else {
+        // f16 C: one row per lane, 64 bytes of the row per chunk; the next chunk's C_old is requested ahead
+        auto load_old = [&](int c, uint4 (&dst)[4]) {
+          const int col0 = tile_col0 + c * 32;
+#pragma unroll
+          for (int v = 0; v < 4; v++) {
+            const int col = col0 + v * 8;
+            dst[v] = (row_ok && c < chunks && col < col_end) ? *reinterpret_cast<const uint4*>(crow + col)
+                                                              : make_uint4(0u, 0u, 0u, 0u);
+          }
+        };
+        uint4 old[4];
+        load_old(half, old);
 #pragma unroll 1
-        for (int c = 0; c < chunks; c++) {
+        for (int c = half; c < chunks; c += 2) {
           uint32_t r[32];
           tmem_ld_32x32b_x32(t_addr + c * 32, r);
           tmem_ld_wait();
@@ -399,9 +434,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             // the two parts of the f16 accumulation are added in f32
 #pragma unroll
             for (int v = 0; v < 32; v++) {
-              const uint32_t pv = __ldcg(part + (c * 32 + v) * 32);
-              if constexpr (ACC_F16) accv[v] += __half2float(__ushort_as_half(static_cast<unsigned short>(pv & 0xFFFF)));
-              else accv[v] += __uint_as_float(pv);
+              if constexpr (ACC_F16) accv[v] += __half2float(__ushort_as_half(static_cast<unsigned short>(pcur[v] & 0xFFFF)));
+              else accv[v] += __uint_as_float(pcur[v]);
+            }
+            if (c + 2 < chunks) {
+#pragma unroll
+              for (int v = 0; v < 32; v++) pcur[v] = __ldcg(part + ((c + 2) * 32 + v) * 32);
             }
           }
           const int col0 = tile_col0 + c * 32;
@@ -410,8 +448,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             for (int v = 0; v < 4; v++) {
               const int col = col0 + v * 8;
               if (col < col_end) {
-                uint4 oldv = *reinterpret_cast<const uint4*>(crow + col);
-                const __half2* oh = reinterpret_cast<const __half2*>(&oldv);
+                const __half2* oh = reinterpret_cast<const __half2*>(&old[v]);
                 uint4 outv;
                 __half2* outh = reinterpret_cast<__half2*>(&outv);
 #pragma unroll
@@ -425,6 +462,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
               }
             }
           }
+          load_old(c + 2, old);
         }
       }
       tc_fence_before_sync();
@@ -451,9 +489,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   if (clock_cta) launch_clock_end(clock_slot, p.status);
 }
 
-// Flags of the stream-K hand-over, [bank][boundary < 128][cta][warp]; a launch uses bank epoch % FLAG_BANKS and
+// Flags of the stream-K hand-over, [bank][boundary < 128][cta][lane quarter][chunk parity]; a launch uses bank epoch % FLAG_BANKS and
 // the value `epoch`, so up to FLAG_BANKS launches may be in flight on one device without clearing anything.
-__device__ uint32_t g_sk_flags[FLAG_BANKS * 128 * 2 * 4];
+__device__ uint32_t g_sk_flags[FLAG_BANKS * 128 * 2 * 4 * 2];
 uint32_t* g_sk_flags_addr[64] = {};
 uint32_t g_epoch = 0;
 
@@ -479,13 +517,31 @@ int pick_pair_bn(int N) {
   return up < 256 ? up : 256;
 }
 
-// Workspace that lets the pair kernel cut its last rounds stream-K style: one partial tile per pair boundary.
+// Pieces per shared tile that minimise the work of the busiest pair when the last full round and the remainder
+// (`shared` tiles on `pairs` pairs) are dealt out in pieces; 1 means sharing gains nothing over whole tiles.
+static int pick_sk_pieces(long long shared, int pairs, int num_kb) {
+  int best_g = 1;
+  double best = static_cast<double>((shared + pairs - 1) / pairs);   // whole tiles: rounds
+  for (int g = 2; g <= 8 && num_kb / g >= SK_MIN_PIECE; g++) {
+    const double load = static_cast<double>((shared * g + pairs - 1) / pairs) / g;
+    if (load < best - 0.05) {   // a gain under 5% of a tile does not pay for the partial tiles
+      best = load;
+      best_g = g;
+    }
+  }
+  return best_g;
+}
+
+// Workspace that lets the pair kernel share out its last rounds stream-K style: one partial tile per pair boundary.
+// 0 when the kernel would not use one for this problem.
 size_t gemm_tc_pair_workspace_bytes(int M, int N, int K, int sm_count) {
   const int pairs = sm_count / 2;
   const int bn = pick_pair_bn(N);
   const long long tiles = static_cast<long long>((M + 2 * BM - 1) / (2 * BM)) * ((N + bn - 1) / bn);
   const int num_kb = (K + BK - 1) / BK;
-  if (pairs < 2 || pairs > 128 || tiles < pairs || tiles % pairs == 0 || num_kb < 2 * SK_MIN_PIECE) return 0;
+  if (pairs < 2 || pairs > MAX_PAIRS || tiles < pairs || tiles % pairs == 0) return 0;
+  if (tiles * num_kb > 0x3fffffffLL) return 0;   // ranges are kept in 32-bit k-block counts
+  if (pick_sk_pieces(pairs + tiles % pairs, pairs, num_kb) == 1) return 0;
   return static_cast<size_t>(pairs) * SK_SLOT_WORDS * 4;
 }
 
@@ -517,6 +573,7 @@ int launch_gemm_tc_pair(const void* A, long long lda, const void* B, long long l
   const int tiles = p.tiles_m * p.tiles_n, pairs = sm_count / 2;
   p.dp_tiles = tiles;
   p.sk_tiles = 0;
+  p.sk_g = 1;
   const size_t need = gemm_tc_pair_workspace_bytes(M, N, K, sm_count);
   int dev = 0;
   if (need > 0 && workspace != nullptr && workspace_bytes >= need && reinterpret_cast<uintptr_t>(workspace) % 256 == 0 &&
@@ -526,9 +583,16 @@ int launch_gemm_tc_pair(const void* A, long long lda, const void* B, long long l
       if (cudaGetSymbolAddress(&fp, g_sk_flags) == cudaSuccess) g_sk_flags_addr[dev] = static_cast<uint32_t*>(fp);
     }
     if (g_sk_flags_addr[dev] != nullptr) {
-      // the last full round and the remainder are shared out by k-blocks
+      // the last full round and the remainder are shared out in pieces
       p.dp_tiles = (tiles / pairs - 1) * pairs;
       p.sk_tiles = tiles - p.dp_tiles;
+      const int num_kb = (K + BK - 1) / BK;
+      p.sk_g = pick_sk_pieces(p.sk_tiles, pairs, num_kb);
+      const long long units = static_cast<long long>(p.sk_tiles) * p.sk_g;
+      for (int i = 0; i <= pairs; i++) {
+        const long long ub = units * i / pairs;
+        p.sk_bound[i] = static_cast<int>((ub / p.sk_g) * num_kb + (ub % p.sk_g) * num_kb / p.sk_g);
+      }
       p.partials = static_cast<uint32_t*>(workspace);
       p.flags = g_sk_flags_addr[dev];
       uint32_t ep = __atomic_add_fetch(&g_epoch, 1u, __ATOMIC_RELAXED);

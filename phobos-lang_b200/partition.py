@@ -212,6 +212,14 @@ def run_partitioned(plan: PartitionPlan, rank: int, a_shard, b_shard, c_block, a
         a_use[i], b_use[i] = a_src, b_src
 
     cctx = torch.cuda.stream(compute_stream) if cuda and compute_stream is not None else _Null()
+    if cuda:
+        # whatever the caller queued on its current stream (filling or restoring the shards and C)
+        # comes before anything this run does on its own streams
+        here = torch.cuda.current_stream()
+        if compute_stream is not None:
+            compute_stream.wait_stream(here)
+        if comm_stream is not None:
+            comm_stream.wait_stream(here)
     if cuda and comm_stream is not None and compute_stream is not None:
         comm_stream.wait_stream(compute_stream)
     stage(0)

@@ -42,22 +42,32 @@ def _check_rows(oracle, torch, A, B, C0, C, rows, alpha, beta, tol, ref_tol, ref
     assert oracle.max_rel_floor(got, want, ref_floor) < ref_tol
 
 
-def test_headline_gemm_fp16tc_fp32acc_4096(ph, oracle, dev):
+@pytest.mark.parametrize("with_workspace", [True, False])
+def test_headline_gemm_fp16tc_fp32acc_4096(ph, oracle, dev, with_workspace):
+    """With the caller's workspace the kernel shares its last 108 tiles between CTA pairs in halves along K
+    (the configuration the benchmark times); without it every tile is computed whole."""
     import torch
     M = N = K = 4096
     A, B, C = _device_inputs(ph, torch, dev, M, N, K, torch.float16, torch.float32, 1.0)
     C0 = C.clone()
-    ph.gemm(A, B, C, 1.0, 0.0, ph.GEMM_FP16TC_FP32ACC)
+    ws = None
+    if with_workspace:
+        nbytes = ph.gemm_workspace_bytes(ph.GEMM_FP16TC_FP32ACC, ph.F16, M, N, K)
+        assert nbytes > 0, "4096^3 must qualify for the shared tail"
+        ws = torch.empty((nbytes,), dtype=torch.uint8, device=dev)
+    ph.gemm(A, B, C, 1.0, 0.0, ph.GEMM_FP16TC_FP32ACC, workspace=ws)
     assert ph.device_status() == 0
-    _check_rows(oracle, torch, A, B, C0, C, _rows(M, 62, 11), 1.0, 0.0, 2e-3, 1e-2, np.sqrt(K) / 3)
+    # rows from all over, plus rows inside the shared tiles (the second raster band: rows 2048 and up)
+    rows = np.unique(np.concatenate([_rows(M, 48, 11), np.arange(2048, 4096, 131, dtype=np.uint64)]))
+    _check_rows(oracle, torch, A, B, C0, C, rows, 1.0, 0.0, 2e-3, 1e-2, np.sqrt(K) / 3)
     # whole output: linear in alpha (alpha = 2 doubles every element exactly: beta = 0, power of two)
     C2 = C0.clone()
-    ph.gemm(A, B, C2, 2.0, 0.0, ph.GEMM_FP16TC_FP32ACC)
+    ph.gemm(A, B, C2, 2.0, 0.0, ph.GEMM_FP16TC_FP32ACC, workspace=ws)
     assert ph.device_status() == 0
     assert torch.equal(C2, 2.0 * C)
     # and a second launch reproduces the first bit for bit
     C3 = C0.clone()
-    ph.gemm(A, B, C3, 1.0, 0.0, ph.GEMM_FP16TC_FP32ACC)
+    ph.gemm(A, B, C3, 1.0, 0.0, ph.GEMM_FP16TC_FP32ACC, workspace=ws)
     assert torch.equal(C3, C)
 
 

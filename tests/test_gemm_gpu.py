@@ -205,11 +205,13 @@ def _workspace(ph, dev, kind, a_dtype, M, N, K):
     return torch.empty((max(n, 256),), dtype=torch.uint8, device=dev), n
 
 
-@pytest.mark.parametrize("shape", [(4864, 1024, 1024), (4864, 1280, 768), (4096, 4096, 1024), (5120, 2304, 520)])
+@pytest.mark.parametrize("shape", [(4864, 1024, 3072), (4864, 1280, 3200), (2560, 2560, 4168), (4864, 1024, 6400),
+                                   (5120, 2304, 3080)])
 def test_gemm_fp16tc_stream_k_tail(ph, oracle, dev, shape):
-    """With a workspace the pair kernel shares out its last rounds of tiles by k-blocks: tiles computed by two CTA
-    pairs (one dumps a partial, the other adds it and runs the epilogue) against tiles computed whole, for tile
-    counts just above one round (76, 95), several rounds (256) and a ragged K (520 = 8 k-blocks + 8)."""
+    """With a workspace the pair kernel shares out its last rounds of tiles in pieces along K: tiles computed by two
+    CTA pairs (one dumps a partial, the other adds it and runs the epilogue) against tiles computed whole.  Tile
+    counts just above one round (76, 95, 100) and above two (180); halves of 24 and 25 k-blocks, quarters
+    (K = 6400), an odd number of k-blocks (4168 = 65 k-blocks + 8) and a ragged last k-block (3080)."""
     import torch
     M, N, K = shape
     a, b, c = _inputs(oracle, M, N, K)
@@ -228,8 +230,8 @@ def test_gemm_fp16tc_stream_k_tail(ph, oracle, dev, shape):
         assert oracle.rel_frobenius(got[rows.astype(int)], want) <= TOL_F16TC
         results.append(got)
     assert np.array_equal(results[0], results[2]), "a relaunch over a used workspace must give the same bits"
-    # with and without the workspace only the summation order of split tiles differs
-    assert oracle.rel_frobenius(results[0], results[1].astype(np.float64)) <= 1e-5
+    # with and without the workspace only the summation order of the shared tiles differs (f32 reassociation)
+    assert oracle.rel_frobenius(results[0], results[1].astype(np.float64)) <= 1e-4
     # the f16-accumulate kernel shares the scheduler
     ch = oracle.fp16_round(c)
     want16 = oracle.gemm_rows(a16, b16, ch, 1.0, 1.0, rows=rows)
@@ -245,9 +247,10 @@ def test_gemm_fp16tc_f32_storage_with_stream_k(ph, oracle, dev):
     """f32-stored operands: the workspace holds the rounded copies first and the kernel's partial tiles after them;
     a workspace that only fits the copies still works (tiles computed whole)."""
     import torch
-    M, N, K = 4864, 1024, 512
+    M, N, K = 4864, 1024, 3072
     a, b, c = _inputs(oracle, M, N, K)
-    want = oracle.gemm_rows(oracle.fp16_round(a), oracle.fp16_round(b), c, 1.0, 0.0)
+    rows = np.arange(0, M, 37, dtype=np.uint64)
+    want = oracle.gemm_rows(oracle.fp16_round(a), oracle.fp16_round(b), c, 1.0, 0.0, rows=rows)
     A, B = _to(dev, a), _to(dev, b)
     full = ph.gemm_workspace_bytes(ph.GEMM_FP16TC_FP32ACC, ph.F32, M, N, K)
     staging = 2 * (M * K + K * N)
@@ -257,7 +260,7 @@ def test_gemm_fp16tc_f32_storage_with_stream_k(ph, oracle, dev):
         C = _to(dev, c)
         ph.gemm(A, B, C, 1.0, 0.0, ph.GEMM_FP16TC_FP32ACC, workspace=ws)
         assert ph.device_status() == 0
-        assert oracle.rel_frobenius(C.cpu().numpy(), want) <= TOL_F16TC
+        assert oracle.rel_frobenius(C.cpu().numpy()[rows.astype(int)], want) <= TOL_F16TC
 
 
 def test_host_pipeline_matches_direct_calls(ph, oracle, dev):
