@@ -163,6 +163,7 @@ class Ctx:
         self.windows = []
         self.cpu_seconds = 1.0   # length of the CPU-baseline sample of the next workload
         self.barrier = None      # N > 1: every timed region starts and ends at a barrier across the ranks
+        self.lean = False        # --kernel-only: the timed launches and nothing else
 
     def time_steps(self, fn_step, steps=None, warmup=None, barrier=None, finish=None):
         """Runs warm-up steps, then times `steps` steps back to back between one pair of CUDA events
@@ -381,6 +382,8 @@ def bench_gemm(ctx: Ctx, name: str, M: int, N: int, K: int, alpha: float, beta: 
                            "peak_source": f"of {peaks['_source']} (burst cuBLAS bf16)",
                            "frac_of_nominal_2250": ach / NOMINAL_F16_TFLOPS,
                            **roofline_common(ctx, name, ach, info.sm_count * 8192.0)}
+    if ctx.lean:
+        return out
     out["parity"] = gemm_parity(ctx, name, kind, M, N, K, alpha, beta, *sets[0], scale, ws)
     if bar:
         out["same_box_bar"] = cublas_bar(ctx, name, M, N, K)
@@ -441,6 +444,8 @@ def bench_flash(ctx: Ctx, BH: int, S: int, D: int, peaks, cpu_baseline=True, e2e
                         "frac_of_nominal_2250": ach / NOMINAL_F16_TFLOPS,
                         **roofline_common(ctx, "flash_fp32" if f32_storage else "flash_fp16", ach,
                                           ph.device_info(dev.index or 0).sm_count * 8192.0)}}
+    if ctx.lean:
+        return out
     out["parity"] = flash_parity(ctx, BH, S, D, Q, K, V, O, scale, ws, f32_storage)
     if f32_storage:
         out["launches_per_step"] = 4      # three f32 -> f16 staging passes and the attention kernel
@@ -491,6 +496,8 @@ def bench_saxpy(ctx: Ctx, n: int, peaks, cpu_baseline=True, e2e=True):
            "roofline": {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
                         "peak_source": f"of {peaks['_source']} (STREAM-style copy)",
                         **{k: v for k, v in roofline_common(ctx, "saxpy_fp32", 0.0, 1.0).items() if k.startswith("traffic")}}}
+    if ctx.lean:
+        return out
     if e2e:
         x, y, o = sets[0]
         hx, hy = pinned_like(torch, x), pinned_like(torch, y)
@@ -743,6 +750,91 @@ def bench_partitioned(ctx: Ctx, world: int, rank: int, MNK: int, alpha: float, b
     return out
 
 
+MATMUL_PH = """
+@cluster(TM in [4096, 16384], TN in [4096, 16384], TK in [4096, 16384])
+@autotune(TM in [32, 128], TN in [32, 128], TK in [4, 16])
+kernel matmul(A: tensor<f32>[M, K], B: tensor<f32>[K, N], C: tensor<f32>[M, N], alpha: f32, beta: f32) {
+  let bi = program_id(0)
+  let bj = program_id(1)
+  var acc: tile<f32>[TM, TN] = 0.0
+  for kk in range(0, K, TK) {
+    acc += dot(A[bi * TM :+ TM, kk :+ TK], B[kk :+ TK, bj * TN :+ TN])
+  }
+  let old = C[bi * TM :+ TM, bj * TN :+ TN]
+  C[bi * TM :+ TM, bj * TN :+ TN] = alpha * acc + beta * old
+}
+"""
+
+
+def bench_plan_driven(ctx: Ctx, world: int, MNK: int, alpha: float, beta: float, steps: int = 2):
+    """The same partitioned matmul through the C ABI only (rank 0 drives it): job text -> phobos_plan_make
+    (HomeLoadPeerFetch over `world` nodes, the reference's default supertiles) -> one executor per GPU, tensors
+    resident in GPU 0's HBM (device:// storage), LOAD / FETCH / STORE as device and peer copies, leaves by entry
+    name.  Time: the longest executor run, on the device (events of each executor's own streams)."""
+    import numpy as np
+    import oracle
+    ph, torch, dev = ctx.ph, ctx.torch, ctx.dev
+    A = torch.empty((MNK, MNK), dtype=torch.float32, device=dev)
+    B = torch.empty((MNK, MNK), dtype=torch.float32, device=dev)
+    C = torch.empty((MNK, MNK), dtype=torch.float32, device=dev)
+    fill_block(ph, A, 1, 0, 0, MNK)
+    fill_block(ph, B, 2, 0, 0, MNK)
+    job = ph.parse_job_text(f"""
+source = matmul.ph
+dim M = {MNK}
+dim N = {MNK}
+dim K = {MNK}
+tensor A = read f32 {MNK}x{MNK} {ph.device_uri(A)}
+tensor B = read f32 {MNK}x{MNK} {ph.device_uri(B)}
+tensor C = rmw  f32 {MNK}x{MNK} {ph.device_uri(C)}
+scalar alpha = f32 {alpha}
+scalar beta = f32 {beta}
+""", "bench job", MATMUL_PH)
+    prog = ph.Program(MATMUL_PH)
+    prog.check_job(job)
+    scalars = {sc.name: ph.PhScalar(0, sc.dtype, sc.bits) for sc in job.scalars}
+    # supertiles: the planner's own cost model (phobos_autotune: NVLink rate, the measured rate of the FFMA leaf, the
+    # arena as the memory limit) ranks the @cluster choices; the best one is planned
+    arena = 12 << 30
+    ranked = ph.autotune(prog, job.dims, world, arena, 770e9, 54e12)
+    supers = ranked[0]["supers"] if ranked else None
+    pl = ph.plan(prog, job.dims, supers=supers, nodes=world, scalars=scalars, policy=ph.HOME_LOAD_PEER_FETCH)
+    pl.validate()
+    tensors = [(t.uri, t.dtype, t.shape, t.mode) for t in job.tensors]
+    times, served = [], 0
+    for it in range(1 + steps):
+        fill_block(ph, C, 3, 0, 0, MNK)
+        torch.cuda.synchronize()
+        exs = [ph.Executor(n, n, arena) for n in range(world)]
+        try:
+            ph.run_plan(pl, prog, tensors, exs)
+            if it > 0:
+                times.append(max(ex.last_run_ms for ex in exs))
+            served = sum(ex.served_bytes for ex in exs)
+        finally:
+            for ex in exs:
+                ex.close()
+    torch.cuda.synchronize()
+    ph.device_status()
+    rows = parity_rows(MNK)
+    got = C[torch.from_numpy(rows).to(dev)].cpu().numpy()
+    oracle.use_all_cores()
+    a = np.concatenate([oracle.lcg_fill_block(1, int(r) * MNK, 1, MNK, MNK) for r in rows])
+    c = np.concatenate([oracle.lcg_fill_block(3, int(r) * MNK, 1, MNK, MNK) for r in rows])
+    b = oracle.lcg_fill(2, MNK * MNK).reshape(MNK, MNK)
+    err = oracle.rel_frobenius(got, oracle.gemm_rows(a, b, c, alpha, beta))
+    del b
+    ms = sum(times) / len(times)
+    shape, grid = pl.super_shape(2)
+    return {"ms_per_step": ms, "tflops": gemm_flops(MNK, MNK, MNK) / (ms * 1e-3) / 1e12,
+            "path": "job text -> phobos_plan_make (HomeLoadPeerFetch) -> one executor per GPU; tensors device-resident "
+                    "on GPU 0; timed on the device per executor, the longest counts",
+            "supertile": list(shape), "output_grid": list(grid), "supers": supers,
+            "predicted_ms": (ranked[0]["makespan_sec"] * 1e3) if ranked else None, "fetch_bytes_planned": pl.fetch_bytes,
+            "fetch_bytes_served": served, "fetch_matches_plan": served == pl.fetch_bytes,
+            "parity": {"rel_frobenius": err, "tol": 1e-5, "rows": int(rows.size), "ok": bool(err <= 1e-5)}}
+
+
 def fill_block(ph, t, seed, row0, col0, pitch):
     """Fills t[r, c] with element (row0 + r) * pitch + col0 + c of the Lcg stream `seed`."""
     ph.fill_random_block(t, seed=seed, first=row0 * pitch + col0, stream_pitch=pitch)
@@ -798,6 +890,9 @@ def main():
     ap.add_argument("--peak-fp16tcf32acc", type=float, default=None,
                     help="TFLOP/s; overrides the f16-tc-f32-acc peak of the CSV")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="with --only: just the timed launches of the workload (no CPU baseline, end-to-end leg, parity "
+                         "check or cuBLAS bar); the command the ncu captures under profiles/ are taken with")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -822,6 +917,11 @@ def main():
     ctx = Ctx(ph, torch, dev, args.steps, args.warmup)
     metric = "GEMM & flash-attn TFLOP/s at 1/2/4/8 B200 and % of dtype roofline"
     cpu = not args.no_cpu
+    if args.kernel_only:
+        if not args.only:
+            raise SystemExit("--kernel-only needs --only WORKLOAD")
+        cpu = False
+        ctx.lean = True
 
     if world > 1 or args.gpus > 1:
         import torch.distributed as dist
@@ -842,6 +942,19 @@ def main():
         # (2) the one configuration that is partitioned across GPUs: matmul_cluster_fp32 16384^3, strong scaling
         ctx.barrier = None
         res = bench_partitioned(ctx, world, rank, 16384, 0.125, 1.5)
+        torch.cuda.empty_cache()
+        # (3) the same problem through the C ABI alone: rank 0 drives one executor per GPU; the other ranks wait on
+        # the host (a key in the rendezvous store), so that no collective kernel sits on their GPUs meanwhile
+        store = dist.distributed_c10d._get_default_store()
+        plan_res = None
+        if rank == 0:
+            try:
+                plan_res = bench_plan_driven(ctx, world, 16384, 0.125, 1.5)
+            finally:
+                store.set("phobos_plan_driven_done", "1")
+        else:
+            store.wait(["phobos_plan_driven_done"])
+        dist.barrier()
         if rank == 0:
             line = {"metric": metric, "value": world * fl / (ms_head * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
                     "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_head,
@@ -865,7 +978,7 @@ def main():
                          else "NCCL broadcast") + ")",
                       "roofline": res["roofline"], "e2e": {k: v for k, v in res["e2e"].items()},
                       "gpu_launches": res["gpu_launches"], "peer_bytes_per_step": res["peer_bytes_per_step"],
-                      "direct_load_bound": res["direct_load_bound"]}
+                      "direct_load_bound": res["direct_load_bound"], "plan_driven": plan_res}
             # the compact summary goes last so that it survives a truncated tail of this line
             summary = {"workload": "matmul_cluster_fp32 16384^3", "scaling": "strong", "value": round(res["tflops"], 2),
                        "unit": "TFLOP/s", "ms_per_step": round(res["ms_per_step"], 3), "grid": res["grid"],
@@ -873,9 +986,14 @@ def main():
                        "efficiency": round(res["efficiency"], 4),
                        "zero_exchange_bound_tflops": round(res["direct_load_bound"]["tflops"], 2),
                        "frac_fp32_peak": round(res["roofline"]["frac"], 4), "parity": res["parity"]}
+            if plan_res:
+                summary["plan_driven_c_abi"] = {"tflops": round(plan_res["tflops"], 2), "ms_per_step": round(plan_res["ms_per_step"], 3),
+                                                "vs_python_orchestrated": round(plan_res["tflops"] / res["tflops"], 4),
+                                                "fetch_matches_plan": plan_res["fetch_matches_plan"],
+                                                "parity_ok": plan_res["parity"]["ok"]}
         dist.barrier()
         sampler.stop()
-        ok = res["parity"]["ok"] and head["parity"]["ok"]
+        ok = res["parity"]["ok"] and head["parity"]["ok"] and (plan_res is None or plan_res["parity"]["ok"])
         if rank == 0:
             line["clocks"] = sampler.summary(ctx.windows)
             line["partitioned_detail"] = detail

@@ -334,6 +334,10 @@ PH_API int phobos_executor_issue(PhExecutor *ex, const PhInstr *instrs, int32_t 
  * Returns 0, or the status of the first failed instruction (engine.rs:744-750). */
 PH_API int phobos_executor_run(PhExecutor *ex);
 PH_API int32_t phobos_executor_drain_completions(PhExecutor *ex, PhCompletion *out, int32_t cap);
+/* Device time of the last successful phobos_executor_run in milliseconds: from an event recorded on the
+ * executor's device when the run started to the last operation it enqueued on any of its streams (CUDA events,
+ * not the host clock; the reference reports elapsed_ns = 0, phobos-pod/src/engine.rs:790).  -1 before any run. */
+PH_API float phobos_executor_last_run_ms(const PhExecutor *ex);
 PH_API uint64_t phobos_executor_arena_used(const PhExecutor *ex);
 PH_API uint64_t phobos_executor_served_bytes(const PhExecutor *ex);  /* phobos-pod/src/server.rs:22 */
 /* Device address and residency of a tile (TileStore::addr/is_resident, tile_store.rs:134-140). */

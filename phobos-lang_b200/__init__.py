@@ -148,6 +148,7 @@ def lib() -> ctypes.CDLL:
             "phobos_executor_issue": (c.c_int, [vp, c.POINTER(PhInstr), i32]),
             "phobos_executor_run": (c.c_int, [vp]),
             "phobos_executor_drain_completions": (i32, [vp, c.POINTER(PhCompletion), i32]),
+            "phobos_executor_last_run_ms": (c.c_float, [vp]),
             "phobos_executor_arena_used": (u64, [vp]),
             "phobos_executor_served_bytes": (u64, [vp]),
             "phobos_executor_tile_addr": (c.c_int, [vp, u64, c.POINTER(vp), c.POINTER(i32)]),
@@ -398,7 +399,7 @@ def size_class(nbytes: int) -> int:
 
 from .job import Job, parse_job, parse_job_text  # noqa: E402
 from .storage import load_region, storage_path, store_region  # noqa: E402
-from .executor import Executor, Instr  # noqa: E402
+from .executor import Executor, Instr, device_uri  # noqa: E402
 from .partition import PartitionPlan, plan_partition  # noqa: E402
 from .hostpipe import HostPipeline  # noqa: E402
 from .planner import (DIRECT_LOAD, HOME_LOAD_PEER_FETCH, NO_BUDGET, Plan, Program, autotune, decode_segment,  # noqa: E402

@@ -117,7 +117,27 @@ struct TensorMetaOwned {
   int dtype;
   std::vector<uint64_t> shape;
   int mode;
+  // device://<gpu>/0x<address>: the tensor lives row-major in that GPU's memory (HBM-resident storage); LOAD and
+  // STORE are then 2-D device copies over NVLink instead of file reads through pinned staging
+  bool on_device = false;
+  int storage_device = -1;
+  char* storage_base = nullptr;
 };
+
+// Parses device://<gpu>/0x<hex address>; false when the URI is of another scheme.
+bool parse_device_uri(const std::string& uri, int* dev, char** base) {
+  if (uri.compare(0, 9, "device://") != 0) return false;
+  char* end = nullptr;
+  const char* p = uri.c_str() + 9;
+  const long d = strtol(p, &end, 10);
+  if (end == p || *end != '/' || d < 0) return false;
+  const char* q = end + 1;
+  const unsigned long long a = strtoull(q, &end, 16);
+  if (end == q || *end != 0 || a == 0) return false;
+  *dev = static_cast<int>(d);
+  *base = reinterpret_cast<char*>(static_cast<uintptr_t>(a));
+  return true;
+}
 
 }  // namespace
 
@@ -139,6 +159,8 @@ struct PhExecutor {
   void* workspace = nullptr;
   size_t workspace_bytes = 0;
   uint64_t served_bytes = 0;
+  cudaEvent_t run_start = nullptr;   // recorded on the device when phobos_executor_run starts
+  float last_run_ms = -1.0f;         // device time from there to the last operation of the run
   int first_failure = 0;
   std::string first_failure_msg;
   // guards the tile table and counters against a peer's FETCH running on another host thread
@@ -250,6 +272,38 @@ bool track(PhExecutor* ex, cudaStream_t s, uint64_t iid, std::vector<uint64_t> w
   return true;
 }
 
+// A region of a device-resident tensor as a 2-D copy: rows x row_bytes at `ptr`, rows `pitch` bytes apart.
+// Returns false (with the error set) when the region does not lie inside the tensor.
+bool device_region(const TensorMetaOwned& m, const PhRegion& rg, size_t es, char** ptr, size_t* pitch, size_t* row_bytes,
+                   size_t* rows) {
+  if (rg.rank == 1) {
+    uint64_t total = 1;
+    for (uint64_t d : m.shape) total *= d;
+    if (rg.offset[0] > total || rg.shape[0] > total - rg.offset[0]) {
+      fail(PH_ERR_INVALID, "region exceeds the tensor's %llu elements", (unsigned long long)total);
+      return false;
+    }
+    *ptr = m.storage_base + rg.offset[0] * es;
+    *pitch = *row_bytes = rg.shape[0] * es;
+    *rows = 1;
+    return true;
+  }
+  if (rg.rank != 2 || m.shape.size() != 2) {
+    fail(PH_ERR_UNSUPPORTED, "device storage supports rank <= 2 regions of rank-2 tensors");
+    return false;
+  }
+  for (int d = 0; d < 2; d++)
+    if (rg.offset[d] > m.shape[d] || rg.shape[d] > m.shape[d] - rg.offset[d]) {
+      fail(PH_ERR_INVALID, "region axis %d exceeds the tensor extent %llu", d, (unsigned long long)m.shape[d]);
+      return false;
+    }
+  *pitch = m.shape[1] * es;
+  *ptr = m.storage_base + rg.offset[0] * *pitch + rg.offset[1] * es;
+  *row_bytes = rg.shape[1] * es;
+  *rows = rg.shape[0];
+  return true;
+}
+
 void do_load(PhExecutor* ex, uint64_t iid, const Node& n) {
   if (n.in.tensor >= ex->tensors.size()) return fail_instr(ex, iid, PH_ERR_STATE, "LOAD of unknown tensor");
   auto t = ex->tiles.find(n.in.tile);
@@ -260,6 +314,20 @@ void do_load(PhExecutor* ex, uint64_t iid, const Node& n) {
   for (int d = 0; d < n.in.region.rank; d++) total *= n.in.region.shape[d];
   if (total != t->second.elems || m.dtype != t->second.dtype)
     return fail_instr(ex, iid, PH_ERR_STATE, "LOAD region does not match the tile");
+  if (m.on_device) {
+    // gather the region's rows into the contiguous tile, device to device (peer copy when the tensor lives on
+    // another GPU); asynchronous, completion by event like every other operation
+    char* src;
+    size_t pitch, row_bytes, rows;
+    if (!device_region(m, n.in.region, es, &src, &pitch, &row_bytes, &rows))
+      return fail_instr(ex, iid, PH_ERR_INVALID, std::string("LOAD: ") + last_error());
+    cudaStream_t s = pick_stream(ex);
+    cudaError_t e = cudaMemcpy2DAsync(reinterpret_cast<void*>(t->second.slab.addr), row_bytes, src, pitch, row_bytes, rows,
+                                      cudaMemcpyDefault, s);
+    if (e != cudaSuccess) return fail_instr(ex, iid, PH_ERR_DEVICE, std::string("LOAD: ") + cudaGetErrorString(e));
+    track(ex, s, iid, {n.in.tile}, nullptr);
+    return;
+  }
   void* stage = nullptr;
   if (cudaMallocHost(&stage, total * es) != cudaSuccess) return fail_instr(ex, iid, PH_ERR_DEVICE, "pinned staging alloc");
   int rc = phobos_storage_load(m.uri.c_str(), m.shape.data(), (int32_t)m.shape.size(), &n.in.region, es, stage);
@@ -287,6 +355,20 @@ void do_store(PhExecutor* ex, uint64_t iid, const Node& n) {
   for (int d = 0; d < n.in.region.rank; d++) total *= n.in.region.shape[d];
   if (total != t->second.elems || m.dtype != t->second.dtype)
     return fail_instr(ex, iid, PH_ERR_STATE, "STORE region does not match the tile");
+  if (m.on_device) {
+    // the producer of the tile has completed (STORE depends on it and completion is event-based), so the scatter
+    // may run on any stream
+    char* dst;
+    size_t pitch, row_bytes, rows;
+    if (!device_region(m, n.in.region, es, &dst, &pitch, &row_bytes, &rows))
+      return fail_instr(ex, iid, PH_ERR_INVALID, std::string("STORE: ") + last_error());
+    cudaStream_t s = pick_stream(ex);
+    cudaError_t e = cudaMemcpy2DAsync(dst, pitch, reinterpret_cast<void*>(t->second.slab.addr), row_bytes, row_bytes, rows,
+                                      cudaMemcpyDefault, s);
+    if (e != cudaSuccess) return fail_instr(ex, iid, PH_ERR_DEVICE, std::string("STORE: ") + cudaGetErrorString(e));
+    track(ex, s, iid, {}, nullptr);
+    return;
+  }
   std::vector<char> host(t->second.elems * es);
   // device-to-host on the executor thread (engine.rs:472-473); all streams are
   // drained first because the producer may have run on any of them
@@ -501,6 +583,7 @@ void phobos_executor_destroy(PhExecutor* ex) {
     if (ex->streams[i]) cudaStreamDestroy(ex->streams[i]);
   if (ex->workspace) cudaFree(ex->workspace);
   if (ex->arena.base) cudaFree(ex->arena.base);
+  if (ex->run_start) cudaEventDestroy(ex->run_start);
   delete ex;
 }
 
@@ -515,6 +598,24 @@ int phobos_executor_set_tensors(PhExecutor* ex, const PhTensorMeta* tensors, int
     m.dtype = tensors[i].dtype;
     m.shape.assign(tensors[i].shape, tensors[i].shape + tensors[i].rank);
     m.mode = tensors[i].mode;
+    if (m.uri.compare(0, 9, "device://") == 0) {
+      if (!parse_device_uri(m.uri, &m.storage_device, &m.storage_base))
+        return fail(PH_ERR_INVALID, "tensor %d: malformed storage URI '%s' (device://<gpu>/0x<address>)", i, m.uri.c_str());
+      int count = 0;
+      if (cudaGetDeviceCount(&count) != cudaSuccess || m.storage_device >= count)
+        return fail(PH_ERR_DEVICE, "tensor %d: no GPU %d", i, m.storage_device);
+      if (m.storage_device != ex->device) {
+        DeviceGuard g(ex->device);
+        int can = 0;
+        cudaDeviceCanAccessPeer(&can, ex->device, m.storage_device);
+        if (!can) return fail(PH_ERR_DEVICE, "tensor %d: GPU %d cannot reach GPU %d", i, ex->device, m.storage_device);
+        cudaError_t e = cudaDeviceEnablePeerAccess(m.storage_device, 0);
+        if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled)
+          return fail(PH_ERR_DEVICE, "enable peer access %d -> %d: %s", ex->device, m.storage_device, cudaGetErrorString(e));
+        cudaGetLastError();
+      }
+      m.on_device = true;
+    }
     ex->tensors.push_back(m);
   }
   return PH_OK;
@@ -591,6 +692,11 @@ int phobos_executor_run(PhExecutor* ex) {
   clear_error();
   if (!ex) return fail(PH_ERR_INVALID, "null executor");
   DeviceGuard g(ex->device);
+  // device-side clock of this run: an event at its start; events after its last operation on every stream
+  if (ex->run_start == nullptr) cudaEventCreate(&ex->run_start);
+  for (int i = 0; i < 4; i++) cudaStreamSynchronize(ex->streams[i]);
+  cudaEventRecord(ex->run_start, ex->streams[0]);
+  ex->last_run_ms = -1.0f;
   int idle_rounds = 0;
   while (true) {
     std::unique_lock<std::mutex> self_lock(ex->mu);
@@ -649,6 +755,20 @@ int phobos_executor_run(PhExecutor* ex) {
     ex->first_failure = 0;
     return code;
   }
+  {
+    float worst = 0.0f;
+    cudaEvent_t end;
+    if (cudaEventCreate(&end) == cudaSuccess) {
+      for (int i = 0; i < 4; i++) {
+        float ms = 0.0f;
+        if (cudaEventRecord(end, ex->streams[i]) == cudaSuccess && cudaEventSynchronize(end) == cudaSuccess &&
+            cudaEventElapsedTime(&ms, ex->run_start, end) == cudaSuccess && ms > worst)
+          worst = ms;
+      }
+      cudaEventDestroy(end);
+      ex->last_run_ms = worst;
+    }
+  }
   return PH_OK;
 }
 
@@ -663,6 +783,7 @@ int32_t phobos_executor_drain_completions(PhExecutor* ex, PhCompletion* out, int
   return n;
 }
 
+float phobos_executor_last_run_ms(const PhExecutor* ex) { return ex ? ex->last_run_ms : -1.0f; }
 uint64_t phobos_executor_arena_used(const PhExecutor* ex) { return ex ? ex->arena.used : 0; }
 uint64_t phobos_executor_served_bytes(const PhExecutor* ex) { return ex ? ex->served_bytes : 0; }
 

@@ -77,10 +77,14 @@ gemm_f32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   const bool clock_cta = threadIdx.x == 0 && blockIdx.x == (gridDim.x - 1 - (gridDim.x >> 2));
   if (clock_cta) launch_clock_begin(clock_slot);
 
-  // tile of this CTA: bands of 8 row-blocks for L2 reuse
+  // Tile of this CTA.  CTAs are dispatched in index order, about two per SM at a time, and the tiles in flight
+  // walk K together, so an A or B k-slab fetched from DRAM by one of them is an L2 hit for the others that
+  // share its row or column block.  DRAM traffic per "wave" is therefore (rows + columns of the block of tiles
+  // in flight) panels: bands of 16 tile rows, odd bands walked right to left, make that block about square
+  // (16 x 18 for 296 tiles in flight; bands of 8 read a third more).
   int mb, nb;
   {
-    constexpr int GROUP = 8;
+    constexpr int GROUP = 16;
     const int t = blockIdx.x;
     const int per_group = GROUP * p.tiles_n;
     const int g = t / per_group;
@@ -89,6 +93,7 @@ gemm_f32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const int r = t - g * per_group;
     mb = first_m + r % gsize;
     nb = r / gsize;
+    if (g & 1) nb = p.tiles_n - 1 - nb;
   }
 
   const int tid = threadIdx.x;

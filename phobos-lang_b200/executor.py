@@ -28,6 +28,15 @@ class Instr:
     _keep: list = field(default_factory=list, repr=False)
 
 
+def device_uri(t) -> str:
+    """Storage URI of a contiguous CUDA tensor that stays alive for the job: `device://<gpu>/0x<address>`.  A job
+    whose tensors carry such URIs keeps them in HBM: LOAD and STORE become 2-D device copies (over NVLink from
+    another GPU) instead of file reads through pinned host memory."""
+    if not t.is_cuda or not t.is_contiguous():
+        raise ValueError("device_uri needs a contiguous CUDA tensor")
+    return f"device://{t.device.index}/0x{t.data_ptr():x}"
+
+
 def instr_array(instrs):
     """[Instr, ...] -> (ctypes array of PhInstr, objects that must stay alive while the array is used)."""
     from . import PhInstr, PhScalar, PhTileArg
@@ -123,6 +132,11 @@ class Executor:
             out.extend((int(buf[i].iid), int(buf[i].status), int(buf[i].elapsed_ns)) for i in range(n))
             if n < 256:
                 return out
+
+    @property
+    def last_run_ms(self) -> float:
+        """Device time (CUDA events) of the last run, from its start to its last operation; -1 before any run."""
+        return float(self._L.phobos_executor_last_run_ms(self._h))
 
     @property
     def arena_used(self) -> int:

@@ -105,6 +105,67 @@ scalar beta = f32 1.5
     assert oracle.rel_frobenius(got, oracle.gemm_rows(a, b, c, 0.125, 1.5)) <= 1e-5
 
 
+@pytest.mark.parametrize("nodes,policy", [(1, "direct"), (2, "fetch"), (4, "fetch")])
+def test_gemm_job_on_device_resident_tensors(ph, oracle, dev, tmp_path, nodes, policy):
+    """The same job with its tensors kept in HBM (`device://<gpu>/0x<address>` storage): LOAD gathers region rows
+    by a 2-D device copy, STORE scatters them back, FETCH is an event-tracked peer copy; nothing passes through
+    the host.  Executors sit on as many GPUs as the box has (all on GPU 0 otherwise)."""
+    import torch
+    M, N, K = 1024, 768, 512
+    a = oracle.lcg_fill(1, M * K).reshape(M, K)
+    b = oracle.lcg_fill(2, K * N).reshape(K, N)
+    c = oracle.lcg_fill(3, M * N).reshape(M, N)
+    A, B, C = (torch.from_numpy(x).to(dev) for x in (a, b, c))
+    (tmp_path / "gemm.ph").write_text(GEMM_PH)
+    (tmp_path / "job.txt").write_text(f"""
+source = {tmp_path}/gemm.ph
+dim M = {M}
+dim N = {N}
+dim K = {K}
+tensor A = read f32 {M}x{K} {ph.device_uri(A)}
+tensor B = read f32 {K}x{N} {ph.device_uri(B)}
+tensor C = rmw  f32 {M}x{N} {ph.device_uri(C)}
+scalar alpha = f32 0.125
+scalar beta = f32 1.5
+""")
+    job = ph.parse_job(str(tmp_path / "job.txt"))
+    prog = ph.Program(job.source)
+    prog.check_job(job)
+    scalars = {s.name: ph.PhScalar(0, s.dtype, s.bits) for s in job.scalars}
+    pl = ph.plan(prog, job.dims, nodes=nodes, scalars=scalars,
+                 policy=ph.HOME_LOAD_PEER_FETCH if policy == "fetch" else ph.DIRECT_LOAD)
+    pl.validate()
+    ndev = torch.cuda.device_count()
+    exs = [ph.Executor(n if n < ndev else 0, n, 16 << 20) for n in range(nodes)]
+    try:
+        assert all(ex.last_run_ms < 0 for ex in exs)
+        ph.run_plan(pl, prog, _tensors(job), exs)
+        for n, ex in enumerate(exs):
+            done = ex.completions()
+            assert sorted(d[0] for d in done) == sorted(i.iid for i in pl.node_instrs(n))
+            assert all(d[1] == 0 for d in done) and ex.arena_used == 0
+            assert ex.last_run_ms >= 0.0
+        if policy == "fetch":
+            assert sum(ex.served_bytes for ex in exs) == pl.fetch_bytes > 0
+    finally:
+        for ex in exs:
+            ex.close()
+    torch.cuda.synchronize()
+    assert oracle.rel_frobenius(C.cpu().numpy(), oracle.gemm_rows(a, b, c, 0.125, 1.5)) <= 1e-5
+    assert torch.equal(A.cpu(), torch.from_numpy(a))        # inputs untouched
+    # a region that leaves the tensor is refused, and so is a malformed address
+    I, tid = ph.Instr, ph.tile_id
+    with ph.Executor(0, 0, 1 << 20) as ex:
+        ex.set_tensors([(ph.device_uri(C), ph.F32, (M, N), ph.RMW)])
+        ex.issue([I(iid=1, op=ph.OP_ALLOC, tile=tid(0, 0, 0), shape=(16, 16), data_type=ph.F32),
+                  I(iid=2, op=ph.OP_LOAD, tile=tid(0, 0, 0), tensor=0, region_offset=(M - 8, 0), region_shape=(16, 16), deps=(1,))])
+        with pytest.raises(ph.PhobosError) as e:
+            ex.run()
+        assert e.value.code == ph.PH_ERR_INVALID
+        with pytest.raises(ph.PhobosError):
+            ex.set_tensors([("device://0/zz", ph.F32, (M, N), ph.RMW)])
+
+
 def test_flash_job_planned_and_executed(ph, oracle, dev, tmp_path):
     """A kernel without a cluster loop is one leaf per query supertile; K and V are loaded whole."""
     Nq, Nk, D = 1024, 640, 128
