@@ -40,7 +40,8 @@
 // two-tile ping-pong is for.  The scale/subtract and the row sums use packed f32x2
 // instructions to halve their issue slots.
 //
-// Measured and not adopted (B4 H32 S4096 D128, this structure at 1108 TFLOP/s):
+// Measured and not adopted (B4 H32 S4096 D128, this structure at 1108 TFLOP/s), each verified
+// against the oracle first:
 //  * P handed over in slices, each with its own barrier, so that O += P V could start
 //    before the block's softmax has finished, with one issuing thread for both tiles:
 //    1043 / 1015 / 867 / 639 TFLOP/s for 1 / 2 / 4 / 8 slices; each hand-over costs a
@@ -49,10 +50,21 @@
 //    (1099), S fetched in two halves with the maximum of the first taken while the
 //    second is on its way (1106), both (1089);
 //  * one or two of every eight exponential pairs as a cubic on the FMA pipes
-//    (2^x = 2^n p(f), relative error 7.5e-5, well inside f16): 1085 / 1074.
+//    (2^x = 2^n p(f), relative error 7.5e-5, well inside f16): 1085 / 1074;
+//  * key blocks of 64 with TWO S buffers per tile (64 + 64 columns, what fits beside O at
+//    D = 128), so that S(n+2) is computed while the softmax works on block n: 997 with one
+//    issuing thread per tile, 1087 with two (one for S = Q K^T, one for O += P V), 967 when
+//    the tiles are also made to take turns at the exponentials.  Clock stamps of that
+//    kernel: a thread needs 70-110 clocks per tcgen05.mma it issues whatever the shape, and
+//    a 64-key block needs 12 of them where a 128-key block needs 16 for twice the keys; from
+//    P(n) handed over to S(n+2) seen by the softmax warps takes 2440 clocks (250 until the
+//    issuer sees P, 280 to issue four MMAs, 350 until the S issuer sees them complete, 550 to
+//    issue eight, 1000 until the last has left the shared in-order pipe and the softmax warp
+//    has woken); both tiles' exponentials fall into step and share the MUFU unit (1250 clocks
+//    per 64 keys).
 // The loop is bound by the dependency chain of a tile, softmax(j) -> P -> O += P V and
 // S(j+1) -> softmax(j+1) (S, P and O of both tiles fill the 512 tensor-memory columns
-// at D = 128, so S cannot be double buffered), not by a pipe.
+// at D = 128, so a 128-key S cannot be double buffered), not by a pipe.
 #include <cuda.h>
 
 #include "common.cuh"
