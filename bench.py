@@ -774,11 +774,17 @@ def bench_plan_driven(ctx: Ctx, world: int, MNK: int, alpha: float, beta: float,
     import numpy as np
     import oracle
     ph, torch, dev = ctx.ph, ctx.torch, ctx.dev
-    A = torch.empty((MNK, MNK), dtype=torch.float32, device=dev)
-    B = torch.empty((MNK, MNK), dtype=torch.float32, device=dev)
-    C = torch.empty((MNK, MNK), dtype=torch.float32, device=dev)
-    fill_block(ph, A, 1, 0, 0, MNK)
-    fill_block(ph, B, 2, 0, 0, MNK)
+    # A, B and C each live whole in one GPU's HBM, on different GPUs where there are that many, so that the
+    # LOADs of the job do not all leave through one GPU's links
+    homes = [torch.device("cuda", k % world) for k in range(3)]
+    tensors_dev = []
+    for seed, home in zip((1, 2, 3), homes):
+        with torch.cuda.device(home):
+            t = torch.empty((MNK, MNK), dtype=torch.float32, device=home)
+            if seed != 3:
+                fill_block(ph, t, seed, 0, 0, MNK)
+            tensors_dev.append(t)
+    A, B, C = tensors_dev
     job = ph.parse_job_text(f"""
 source = matmul.ph
 dim M = {MNK}
@@ -803,8 +809,10 @@ scalar beta = f32 {beta}
     tensors = [(t.uri, t.dtype, t.shape, t.mode) for t in job.tensors]
     times, served = [], 0
     for it in range(1 + steps):
-        fill_block(ph, C, 3, 0, 0, MNK)
-        torch.cuda.synchronize()
+        with torch.cuda.device(homes[2]):
+            fill_block(ph, C, 3, 0, 0, MNK)
+        for home in homes:
+            torch.cuda.synchronize(home)
         exs = [ph.Executor(n, n, arena) for n in range(world)]
         try:
             ph.run_plan(pl, prog, tensors, exs)
@@ -814,10 +822,12 @@ scalar beta = f32 {beta}
         finally:
             for ex in exs:
                 ex.close()
-    torch.cuda.synchronize()
-    ph.device_status()
+    for n in range(world):
+        torch.cuda.synchronize(n)
+        with torch.cuda.device(n):
+            ph.device_status()
     rows = parity_rows(MNK)
-    got = C[torch.from_numpy(rows).to(dev)].cpu().numpy()
+    got = C[torch.from_numpy(rows).to(C.device)].cpu().numpy()
     oracle.use_all_cores()
     a = np.concatenate([oracle.lcg_fill_block(1, int(r) * MNK, 1, MNK, MNK) for r in rows])
     c = np.concatenate([oracle.lcg_fill_block(3, int(r) * MNK, 1, MNK, MNK) for r in rows])
@@ -827,8 +837,9 @@ scalar beta = f32 {beta}
     ms = sum(times) / len(times)
     shape, grid = pl.super_shape(2)
     return {"ms_per_step": ms, "tflops": gemm_flops(MNK, MNK, MNK) / (ms * 1e-3) / 1e12,
-            "path": "job text -> phobos_plan_make (HomeLoadPeerFetch) -> one executor per GPU; tensors device-resident "
-                    "on GPU 0; timed on the device per executor, the longest counts",
+            "path": "job text -> phobos_plan_make (HomeLoadPeerFetch) -> one executor per GPU; A, B, C device-resident, "
+                    "each whole on one GPU (" + ", ".join(str(h) for h in homes) + "); timed on the device per "
+                    "executor, the longest counts",
             "supertile": list(shape), "output_grid": list(grid), "supers": supers,
             "predicted_ms": (ranked[0]["makespan_sec"] * 1e3) if ranked else None, "fetch_bytes_planned": pl.fetch_bytes,
             "fetch_bytes_served": served, "fetch_matches_plan": served == pl.fetch_bytes,
