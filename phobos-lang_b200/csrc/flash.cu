@@ -62,9 +62,28 @@
 //    issue eight, 1000 until the last has left the shared in-order pipe and the softmax warp
 //    has woken); both tiles' exponentials fall into step and share the MUFU unit (1250 clocks
 //    per 64 keys).
+//  * ONE 128-row tile per CTA with THREE 128-key S buffers beside O (a persistent CTA walks its
+//    tiles; separate issuing threads for S = Q K^T and O += P V; separate K and Q/V producers),
+//    so that S(n+1), S(n+2) are computed while the softmax works on block n.  Four forms, all
+//    parity-green: both warpgroups on every block, each thread taking 64 of its row's keys and
+//    exchanging the row maximum through shared memory (917); the warpgroups on alternate blocks,
+//    the reference maximum handed from block to block, dedicated epilogue warps (972; 1005 with
+//    the hand-over in one tagged word; 951 with hardware-suspending waits); the column split
+//    again with the softmax loop software pipelined two blocks deep (753).  Clock stamps: every
+//    shared-memory round trip of a softmax warp (an mbarrier that has long completed, a flag
+//    word) costs 300-500 clocks while S = Q K^T streams both operands from shared memory at the
+//    full 128 B/clk, and those forms need two or three of them per block where this kernel needs
+//    one; a block's buffer is held for softmax + 2400 clocks (P seen by the issuer, 8 MMAs, the
+//    commit seen by the other issuer, 8 MMAs, S seen), so three buffers give a period of
+//    (softmax + 2400) / 3 >= 1900 clocks per block, no better than the 1920 of this kernel.
+//  * The exponential loop on its own (register data, idle SM): 1180 clocks per 128 keys for one
+//    warp per scheduler, 1050 per block with two (the MUFU floor is 1024: 4096 ex2 per scheduler
+//    at 4 per clock); with 2/8 or 3/8 of the pairs as a cubic on the FMA/ALU pipes 1080 and 920:
+//    the polynomial costs nearly the issue slots and ALU cycles it saves in MUFU cycles.
 // The loop is bound by the dependency chain of a tile, softmax(j) -> P -> O += P V and
 // S(j+1) -> softmax(j+1) (S, P and O of both tiles fill the 512 tensor-memory columns
-// at D = 128, so a 128-key S cannot be double buffered), not by a pipe.
+// at D = 128, so a 128-key S cannot be double buffered without giving up the second tile),
+// with the exponentials of one warp per scheduler at the MUFU rate inside it.
 #include <cuda.h>
 
 #include "common.cuh"
