@@ -43,11 +43,35 @@ KERNEL_FILES = {"gemm_fp16tc_fp32acc": "gemm_tc2.cu", "gemm_fp16": "gemm_tc2.cu"
                 "matmul_cluster_fp32": "gemm_f32.cu", "flash_fp16": "flash.cu", "saxpy_fp32": "elementwise.cu"}
 
 
+def _code_only(text):
+    """C++ source without comments and blank space, so that a change of wording does not look like a change of
+    the kernel.  String literals are kept as they are."""
+    out, i, n = [], 0, len(text)
+    while i < n:
+        c = text[i]
+        if c == '"':
+            j = i + 1
+            while j < n and text[j] != '"':
+                j += 2 if text[j] == "\\" else 1
+            out.append(text[i:j + 1])
+            i = j + 1
+        elif text.startswith("//", i):
+            while i < n and text[i] != "\n":
+                i += 1
+        elif text.startswith("/*", i):
+            i = text.index("*/", i) + 2
+        else:
+            out.append(c)
+            i += 1
+    return "".join("".join(out).split())
+
+
 def kernel_sha(name):
-    """First 12 hex digits of the SHA-256 of the kernel source that serves a workload."""
+    """First 12 hex digits of the SHA-256 of the code (comments and blank space removed) of the kernel source that
+    serves a workload."""
     import hashlib
     f = ROOT / "phobos-lang_b200" / "csrc" / KERNEL_FILES[name]
-    return hashlib.sha256(f.read_bytes()).hexdigest()[:12]
+    return hashlib.sha256(_code_only(f.read_text()).encode()).hexdigest()[:12]
 
 
 def ncu_traffic(name):
