@@ -207,6 +207,7 @@ int phobos_device_status(void* stream, uint32_t* status_out) {
 size_t phobos_gemm_workspace_bytes(int32_t kind, int32_t a_dtype, int64_t M, int64_t N, int64_t K) {
   if (M <= 0 || N <= 0 || K <= 0 || M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return 0;
   size_t bytes = 0;
+  if (kind == PH_GEMM_FP32) return gemm_f32_workspace_bytes(M, K);
   if (kind == PH_GEMM_FP16TC_FP32ACC && a_dtype == PH_F32) bytes += gemm_staging_bytes(M, N, K);
   if (kind == PH_GEMM_FP16TC_FP32ACC || kind == PH_GEMM_FP16) {
     const int sms = sm_count_or_default();
@@ -232,9 +233,12 @@ int phobos_gemm(const PhTensor* A, const PhTensor* B, const PhTensor* C, float a
     case PH_GEMM_FP32: {
       if (a.dtype != PH_F32 || b.dtype != PH_F32 || c.dtype != PH_F32)
         return fail(PH_ERR_INVALID, "gemm_fp32 takes f32 A, B and C");
+      if (workspace && reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
+        return fail(PH_ERR_WORKSPACE, "workspace is not 256-byte aligned");
+      // optional: with room for a transposed copy of A the faster form of the kernel runs
       rc = launch_gemm_f32(reinterpret_cast<const float*>(a.base), a.ld, reinterpret_cast<const float*>(b.base), b.ld,
-                           reinterpret_cast<float*>(c.base), c.ld, (int)M, (int)N, (int)K, alpha, beta, ds->status,
-                           stream, &err);
+                           reinterpret_cast<float*>(c.base), c.ld, (int)M, (int)N, (int)K, alpha, beta, workspace,
+                           workspace ? workspace_bytes : 0, ds->status, stream, &err);
       return map_launch_rc(rc, "gemm_fp32", err);
     }
     case PH_GEMM_FP16TC_FP32ACC: {

@@ -158,7 +158,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                  const __grid_constant__ CUtensorMap tmV, FlashParams p) {
   using C_ = FCfg<D>;
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // rounded up to 1024 B as an offset into the array: a pointer rebuilt from an integer would lose the
+  // shared address space and turn every access through it into a generic load or store
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   // K and V blocks share one ring of RING slots, filled in consumption order
   // K0 V0 K1 V1 ...: item n (K_j = 2j, V_j = 2j+1) lives in slot n % RING.
   constexpr int RING = C_::RING;

@@ -10,20 +10,29 @@
 // to a sequential f32 fma chain.
 //
 // Structure: CTA tile 128x128, K step 16, 128 threads, 8 rows x 16 columns of outputs per
-// thread in registers (128 accumulators as 64 packed pairs), two CTAs per SM.  A [128 x 16]
-// and B [16 x 128] tiles are staged by TMA into a ring of shared-memory stages; a `full`
-// mbarrier per stage signals arrival and an `empty` mbarrier (one arrival per warp) lets the
-// refill proceed without a CTA-wide barrier, so warps drift apart by up to a stage.  The A
-// tile is stored 64B-swizzled so that the rows a warp reads in one instruction land in
-// different banks.  The multiply-adds are issued as packed fma.rn.f32x2 (two independent
-// IEEE fmas per instruction): the math is unchanged while the instruction count halves.
+// thread in registers (128 accumulators as 64 packed pairs), two CTAs per SM.  A and B tiles
+// of 16 k are staged by TMA into a ring of shared-memory stages; a `full` mbarrier per stage
+// signals arrival and an `empty` mbarrier (one arrival per warp) lets the refill proceed
+// without a CTA-wide barrier, so warps drift apart by up to a stage.  The multiply-adds are
+// issued as packed fma.rn.f32x2 (two independent IEEE fmas per instruction): the math is
+// unchanged while the instruction count halves.
+//
+// Two forms of the same kernel, bit-identical results:
+//  * AT (the caller gave workspace): a pass first writes A transposed, [K][M], into the
+//    workspace, and the A tile lands in shared memory as [k][m].  A thread then fetches its
+//    eight rows of one k with two 128-bit loads, as it fetches its sixteen columns of B with
+//    four, and 24 fragment registers per k leave the compiler room to run the loads well ahead
+//    of the multiply-adds.  The inner loop alone (shared memory preloaded, no barriers) runs at
+//    67 TFLOP/s on a B200, 0.90 of the FFMA peak.
+//  * in place (no workspace): the A tile is [m][k] as it lies in memory, 64B-swizzled so that
+//    the rows a warp reads land in different banks; eight scalar loads per k (the inner loop
+//    alone reaches 59-60 TFLOP/s in this layout whether the loads are scalar or 128-bit over
+//    four k, which then hold 32 registers).
 //
 // Why 8 x 16 per thread: a shared-memory wavefront delivers 4 bytes per lane, so a thread
 // tile of r x c outputs needs r + c wavefronts per k for r * c fmas.  The SM does 128 fmas
 // and 1 wavefront per clock, i.e. 4 fmas per lane per wavefront at balance: an 8 x 8 tile
-// sits exactly on that line (measured: 540 M shared wavefronts, the load pipe as busy as
-// the FMA pipe, 48 TFLOP/s), 8 x 16 needs 24 wavefronts per 128 fmas (75 %; 52 TFLOP/s).
-// The price is 255 registers per thread, hence two warps per scheduler.
+// sits exactly on that line, 8 x 16 needs 24 wavefronts per 128 fmas (75 %).
 #include <cuda.h>
 
 #include "common.cuh"
@@ -64,10 +73,14 @@ __device__ __forceinline__ float2 unpack2(unsigned long long v) {
   return r;
 }
 
+// AT: the A operand is the transposed copy [K][M] and its tile lands as [k][m].
+template <bool AT>
 __global__ void __launch_bounds__(THREADS, 2)
 gemm_f32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, F32Params p) {
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // rounded up to 1024 B as an offset into the array, so that the compiler still knows the address space
+  // (a pointer rebuilt from an integer turns every fragment load into a generic load)
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
   uint64_t* empty = full + STAGES;
   volatile uint32_t* abort_flag = reinterpret_cast<uint32_t*>(empty + STAGES);
@@ -98,10 +111,14 @@ gemm_f32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
-  // warp tile 64 rows x 64 cols; warps arranged 2 (rows) x 2 (cols); 8 rows x 16 columns per thread
-  const int wrow = (warp >> 1) * 64, wcol = (warp & 1) * 64;
-  const int ty = lane >> 2;  // 0..7 : rows  wrow + ty + 8*i
-  const int tx = lane & 3;   // 0..3 : cols  wcol + tx*4 + 16*j + (0..3)
+  // In place: warp tile 64 x 64, warps 2 x 2; a thread has rows wrow + ty + 8*i and columns
+  // wcol + 4*tx + 16*j + (0..3).
+  // AT: a thread has rows 4*ty + (0..3) and 64 + 4*ty + (0..3), columns 4*tx + 32*j + (0..3), with
+  // tx = tid % 8 and ty = tid / 8: both fragments of a k are 128-bit loads, and a warp stores whole
+  // 128-byte row segments of C.
+  const int wrow = AT ? 0 : (warp >> 1) * 64, wcol = AT ? 0 : (warp & 1) * 64;
+  const int ty = AT ? (tid >> 3) : (lane >> 2);
+  const int tx = AT ? (tid & 7) : (lane & 3);
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; s++) {
@@ -118,24 +135,28 @@ gemm_f32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   const int num_kb = (p.K + BK - 1) / BK;
   auto issue = [&](int kb, int stage) {
     mbar_arrive_expect_tx(&full[stage], STAGE_BYTES);
-    tma_load_2d(smem + stage * STAGE_BYTES, &tmA, &full[stage], kb * BK, mb * BM);
+    if constexpr (AT) tma_load_2d(smem + stage * STAGE_BYTES, &tmA, &full[stage], mb * BM, kb * BK);
+    else tma_load_2d(smem + stage * STAGE_BYTES, &tmA, &full[stage], kb * BK, mb * BM);
     tma_load_2d(smem + stage * STAGE_BYTES + A_BYTES, &tmB, &full[stage], nb * BN, kb * BK);
   };
   if (tid == 0) {
     for (int s = 0; s < STAGES && s < num_kb; s++) issue(s, s);
   }
 
-  // acc[i][jp]: row wrow + ty + 8*i, column pair jp (columns 2*jp, 2*jp+1 of the thread's 16)
+  // acc[i][jp]: i-th row of the thread, column pair jp (columns 2*jp, 2*jp+1 of the thread's 16)
   unsigned long long acc[8][8];
 #pragma unroll
   for (int i = 0; i < 8; i++)
 #pragma unroll
     for (int jp = 0; jp < 8; jp++) acc[i][jp] = 0ull;  // two +0.0f
 
-  // byte offset of row (wrow + ty + 4*i) in an A tile and its swizzle term:
-  // row r lives at r*64 B, its 16-byte chunk c at chunk (c ^ ((r >> 1) & 3))  (TMA 64B swizzle)
-  const int a_row_base = (wrow + ty) * 64;
-  const int b_col_base = (wcol + tx * 4) * 4;
+  // In place: byte offset of the thread's first row in an A tile; row r lives at r*64 B, its 16-byte chunk c
+  // at chunk (c ^ ((r >> 1) & 3)) (TMA 64B swizzle), and that term is the same for the thread's eight rows.
+  const int a_row_base = AT ? ty * 16 : (wrow + ty) * 64;
+  const int b_col_base = AT ? tx * 16 : (wcol + tx * 4) * 4;
+  uint32_t a_sw[4];
+#pragma unroll
+  for (int kc = 0; kc < 4; kc++) a_sw[kc] = static_cast<uint32_t>((kc ^ (((wrow + ty) >> 1) & 3)) << 4);
 
   int stage = 0;
   uint32_t phase = 0;
@@ -153,32 +174,60 @@ gemm_f32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
     const uint8_t* sA = smem + stage * STAGE_BYTES;
     const uint8_t* sB = smem + stage * STAGE_BYTES + A_BYTES;
+    if constexpr (AT) {
 #pragma unroll
-    for (int k2 = 0; k2 < BK / 2; k2++) {
-      // two k at a time: a 64-bit load per row (rows of a warp sit in different banks thanks to
-      // the swizzle), four 128-bit loads of B per k
-      const int kc = k2 >> 1, half = k2 & 1;
-      float2 a[8];
-#pragma unroll
-      for (int i = 0; i < 8; i++) {
-        const int r = wrow + ty + 8 * i;
-        a[i] = *reinterpret_cast<const float2*>(sA + a_row_base + i * 512 + ((kc ^ ((r >> 1) & 3)) << 4) + half * 8);
-      }
-#pragma unroll
-      for (int kk = 0; kk < 2; kk++) {
-        const uint8_t* brow = sB + (k2 * 2 + kk) * (BN * 4) + b_col_base;
+      for (int k = 0; k < BK; k++) {
+        const float4 a0 = *reinterpret_cast<const float4*>(sA + k * (BM * 4) + a_row_base);
+        const float4 a1 = *reinterpret_cast<const float4*>(sA + k * (BM * 4) + a_row_base + 256);
         ulonglong2 b[4];
 #pragma unroll
-        for (int j = 0; j < 4; j++) b[j] = *reinterpret_cast<const ulonglong2*>(brow + j * 64);
+        for (int j = 0; j < 4; j++) b[j] = *reinterpret_cast<const ulonglong2*>(sB + k * (BN * 4) + b_col_base + j * 128);
+        const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
 #pragma unroll
         for (int i = 0; i < 8; i++) {
-          const unsigned long long a2 = dup2(kk == 0 ? a[i].x : a[i].y);
+          const unsigned long long a2 = dup2(av[i]);
 #pragma unroll
           for (int j = 0; j < 4; j++) {
             ffma2(acc[i][2 * j], a2, b[j].x);
             ffma2(acc[i][2 * j + 1], a2, b[j].y);
           }
         }
+      }
+    } else {
+      // one k at a time: eight scalar loads of A (the four lanes of a row share the word) and four 128-bit
+      // loads of B; the fragments of k+1 are fetched before the multiply-adds of k are issued
+      const uint32_t sA32 = smem_u32(sA) + a_row_base;
+      const uint32_t sB32 = smem_u32(sB) + b_col_base;
+      float a_cur[8], a_nxt[8];
+      ulonglong2 b_cur[4], b_nxt[4];
+      auto load_frag = [&](int k, float (&a)[8], ulonglong2 (&b)[4]) {
+        const uint32_t aoff = a_sw[k >> 2] + (k & 3) * 4;
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+          asm volatile("ld.shared.f32 %0, [%1];" : "=f"(a[i]) : "r"(sA32 + aoff + i * 512));
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+          asm volatile("ld.shared.v2.u64 {%0, %1}, [%2];"
+                       : "=l"(b[j].x), "=l"(b[j].y)
+                       : "r"(sB32 + k * (BN * 4) + j * 64));
+      };
+      load_frag(0, a_cur, b_cur);
+#pragma unroll
+      for (int k = 0; k < BK; k++) {
+        if (k + 1 < BK) load_frag(k + 1, a_nxt, b_nxt);
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          const unsigned long long a2 = dup2(a_cur[i]);
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            ffma2(acc[i][2 * j], a2, b_cur[j].x);
+            ffma2(acc[i][2 * j + 1], a2, b_cur[j].y);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) a_cur[i] = a_nxt[i];
+#pragma unroll
+        for (int j = 0; j < 4; j++) b_cur[j] = b_nxt[j];
       }
     }
     // this warp is done with the stage
@@ -193,12 +242,12 @@ gemm_f32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   if (ok) {
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-      const int row = mb * BM + wrow + ty + 8 * i;
+      const int row = mb * BM + (AT ? 4 * ty + (i & 3) + 64 * (i >> 2) : wrow + ty + 8 * i);
       if (row < p.M) {
         float* crow = p.C + static_cast<long long>(row) * p.ldc;
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-          const int col = nb * BN + wcol + tx * 4 + 16 * j;
+          const int col = nb * BN + (AT ? 4 * tx + 32 * j : wcol + tx * 4 + 16 * j);
           if (col < p.N) {  // N is a multiple of 4
             const float4 old = *reinterpret_cast<const float4*>(crow + col);
             const float2 lo = unpack2(acc[i][2 * j]), hi = unpack2(acc[i][2 * j + 1]);
@@ -218,6 +267,25 @@ gemm_f32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
   }
   if (clock_cta) launch_clock_end(clock_slot, p.status);
+}
+
+// At[k][m] = A[m][k]: 32 x 32 tiles through shared memory, both sides coalesced.
+__global__ void __launch_bounds__(256) transpose_f32_kernel(const float* __restrict__ A, long long lda,
+                                                            float* __restrict__ At, long long ldt, int M, int K) {
+  __shared__ float tile[32][33];
+  const int k0 = blockIdx.x * 32, m0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 32 x 8
+#pragma unroll
+  for (int r = ty; r < 32; r += 8) {
+    const int m = m0 + r, k = k0 + tx;
+    tile[r][tx] = (m < M && k < K) ? A[static_cast<long long>(m) * lda + k] : 0.0f;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = ty; r < 32; r += 8) {
+    const int k = k0 + r, m = m0 + tx;
+    if (k < K && m < M) At[static_cast<long long>(k) * ldt + m] = tile[tx][r];
+  }
 }
 
 // C = beta * C, or C = 0 (matmul_init leaf).  One float4 per thread per step.
@@ -244,11 +312,22 @@ __global__ void scale_f32_kernel(float* C, long long ldc, long long rows, long l
 
 }  // namespace
 
+size_t gemm_f32_workspace_bytes(long long M, long long K) {
+  const long long ldt = (M + 3) / 4 * 4;
+  return (static_cast<size_t>(K) * ldt * 4 + 255) & ~static_cast<size_t>(255);
+}
+
 int launch_gemm_f32(const float* A, long long lda, const float* B, long long ldb, float* C, long long ldc, int M,
-                    int N, int K, float alpha, float beta, uint32_t* status, cudaStream_t stream, const char** err) {
+                    int N, int K, float alpha, float beta, void* workspace, size_t workspace_bytes, uint32_t* status,
+                    cudaStream_t stream, const char** err) {
+  // with room for a transposed copy of A the A tile is read as [k][m]
+  const bool at = workspace != nullptr && workspace_bytes >= gemm_f32_workspace_bytes(M, K) &&
+                  reinterpret_cast<uintptr_t>(workspace) % 256 == 0;
+  const long long ldt = (static_cast<long long>(M) + 3) / 4 * 4;
   CUtensorMap tmA, tmB;
-  if (!make_tmap_2d(&tmA, A, TMAP_F32, M, K, lda, BM, BK, TMAP_SWIZZLE_64B) ||
-      !make_tmap_2d(&tmB, B, TMAP_F32, K, N, ldb, BK, BN, TMAP_SWIZZLE_NONE)) {
+  const bool maps = at ? make_tmap_2d(&tmA, workspace, TMAP_F32, K, M, ldt, BK, BM, TMAP_SWIZZLE_NONE)
+                       : make_tmap_2d(&tmA, A, TMAP_F32, M, K, lda, BM, BK, TMAP_SWIZZLE_64B);
+  if (!maps || !make_tmap_2d(&tmB, B, TMAP_F32, K, N, ldb, BK, BN, TMAP_SWIZZLE_NONE)) {
     *err = "cuTensorMapEncodeTiled failed (alignment or driver entry point)";
     return -1;
   }
@@ -263,10 +342,22 @@ int launch_gemm_f32(const float* A, long long lda, const float* B, long long ldb
   p.C = C;
   p.ldc = ldc;
   p.status = status;
-  cudaError_t e = cudaFuncSetAttribute(gemm_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-  if (e == cudaSuccess) {
-    gemm_f32_kernel<<<p.tiles_m * p.tiles_n, THREADS, SMEM_BYTES, stream>>>(tmA, tmB, p);
+  cudaError_t e;
+  if (at) {
+    dim3 tgrid((K + 31) / 32, (M + 31) / 32);
+    transpose_f32_kernel<<<tgrid, 256, 0, stream>>>(A, lda, static_cast<float*>(workspace), ldt, M, K);
     e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_f32_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e == cudaSuccess) {
+      gemm_f32_kernel<true><<<p.tiles_m * p.tiles_n, THREADS, SMEM_BYTES, stream>>>(tmA, tmB, p);
+      e = cudaGetLastError();
+    }
+  } else {
+    e = cudaFuncSetAttribute(gemm_f32_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e == cudaSuccess) {
+      gemm_f32_kernel<false><<<p.tiles_m * p.tiles_n, THREADS, SMEM_BYTES, stream>>>(tmA, tmB, p);
+      e = cudaGetLastError();
+    }
   }
   if (e != cudaSuccess) {
     *err = cudaGetErrorString(e);

@@ -51,9 +51,13 @@ bool make_tmap_2d(void* tmap_out, const void* base, TmapType type, long long row
 bool make_tmap_3d(void* tmap_out, const void* base, TmapType type, long long batch, long long rows, long long cols,
                   long long ld_elems, long long batch_pitch_elems, int box_rows, int box_cols, TmapSwizzle swizzle);
 
-// gemm_f32.cu — FFMA GEMM and the matmul_init leaf.
+// gemm_f32.cu — FFMA GEMM and the matmul_init leaf.  With `workspace` of at least
+// gemm_f32_workspace_bytes(M, K) bytes (256-byte aligned) a transposed copy of A is written there first and
+// the faster form of the kernel runs; the result is bit-identical either way.
+size_t gemm_f32_workspace_bytes(long long M, long long K);
 int launch_gemm_f32(const float* A, long long lda, const float* B, long long ldb, float* C, long long ldc, int M,
-                    int N, int K, float alpha, float beta, uint32_t* status, cudaStream_t stream, const char** err);
+                    int N, int K, float alpha, float beta, void* workspace, size_t workspace_bytes, uint32_t* status,
+                    cudaStream_t stream, const char** err);
 int launch_scale_f32(float* C, long long ldc, long long rows, long long cols, float beta, bool zero_fill,
                      cudaStream_t stream, const char** err);
 
