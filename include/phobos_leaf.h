@@ -113,8 +113,15 @@ PH_API int phobos_device_status(void *stream, uint32_t *status_out);
  * COMPUTE of phobos-pod/src/engine.rs:542-653.  A[M,K], B[K,N], C[M,N],
  * row-major.  C is read even when beta == 0 (the reference computes
  * 0*C_old; phobos-lang/src/codegen/matmul.rs:393-402).  Non-blocking.
- * `workspace` is only needed for PH_GEMM_FP16TC_FP32ACC with f32-stored A/B
- * (rounded copies); size from phobos_gemm_workspace_bytes.                    */
+ * `workspace` (256-byte aligned, phobos_gemm_workspace_bytes bytes) is
+ * REQUIRED for PH_GEMM_FP16TC_FP32ACC with f32-stored A/B (the rounded copies)
+ * and OPTIONAL otherwise: the tensor-core kinds use it to share their last
+ * rounds of tiles between CTA pairs, PH_GEMM_FP32 writes a transposed copy of
+ * A there and runs the faster form of its kernel (about 1.1x; without it, or
+ * with less than the size asked for, A is read in place).  The result does
+ * not depend on it for PH_GEMM_FP32 (bit-identical), and only in the order of
+ * two f32 partial sums for the tensor-core kinds.  Calls that share a
+ * workspace must not overlap on the GPU.                                      */
 PH_API int phobos_gemm(const PhTensor *A, const PhTensor *B, const PhTensor *C, float alpha, float beta,
                        int32_t kind, void *workspace, size_t workspace_bytes, void *stream);
 PH_API size_t phobos_gemm_workspace_bytes(int32_t kind, int32_t a_dtype, int64_t M, int64_t N, int64_t K);

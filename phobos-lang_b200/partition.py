@@ -323,14 +323,24 @@ def make_groups(plan: PartitionPlan, rank: int, max_ctas: int = 0):
 
 
 def cuda_leaves():
-    """The native leaves: `matmul_init` and `matmul` (beta = 1) through the C ABI."""
-    from . import GEMM_FP32, gemm, matmul_init
+    """The native leaves: `matmul_init` and `matmul` (beta = 1) through the C ABI.  The step leaf owns one
+    workspace that grows to the largest step it has seen (the steps of a rank run one after another on the
+    compute stream, so they may share it); with it the FFMA kernel reads a transposed copy of the A block."""
+    import torch
+
+    from . import F32, GEMM_FP32, gemm, gemm_workspace_bytes, matmul_init
+
+    state = {"ws": None}
 
     def leaf_init(C, beta):
         matmul_init(C, beta)
 
     def leaf_step(A, B, C, alpha):
-        gemm(A, B, C, alpha, 1.0, GEMM_FP32)
+        need = gemm_workspace_bytes(GEMM_FP32, F32, A.shape[0], B.shape[1], A.shape[1])
+        ws = state["ws"]
+        if need and (ws is None or ws.numel() < need or ws.device != A.device):
+            ws = state["ws"] = torch.empty((need,), dtype=torch.uint8, device=A.device)
+        gemm(A, B, C, alpha, 1.0, GEMM_FP32, workspace=ws if need else None)
 
     return leaf_init, leaf_step
 

@@ -72,16 +72,23 @@ def test_headline_gemm_fp16tc_fp32acc_4096(ph, oracle, dev, with_workspace):
 
 
 def test_gemm_fp32_4096(ph, oracle, dev):
+    """Both forms of the FFMA kernel at the benchmark size: A read in place, and A read from the transposed
+    copy in the caller's workspace."""
     import torch
     M = N = K = 4096
     A, B, C = _device_inputs(ph, torch, dev, M, N, K, torch.float32, torch.float32, 1.0)
+    ws = torch.empty((ph.gemm_workspace_bytes(ph.GEMM_FP32, ph.F32, M, N, K),), dtype=torch.uint8, device=dev)
     C0 = C.clone()
-    ph.gemm(A, B, C, 0.125, 1.5, ph.GEMM_FP32)
+    ph.gemm(A, B, C, 0.125, 1.5, ph.GEMM_FP32, workspace=ws)
     assert ph.device_status() == 0
     _check_rows(oracle, torch, A, B, C0, C, _rows(M, 62, 12), 0.125, 1.5, 1e-5, 1e-3, 1.0)
+    Cp = C0.clone()
+    ph.gemm(A, B, Cp, 0.125, 1.5, ph.GEMM_FP32)
+    assert ph.device_status() == 0
+    assert torch.equal(Cp, C), "the two forms of the kernel differ"
     # whole output: with beta = 0 and alpha a power of two the result scales exactly
     Ca, Cb = C0.clone(), C0.clone()
-    ph.gemm(A, B, Ca, 1.0, 0.0, ph.GEMM_FP32)
+    ph.gemm(A, B, Ca, 1.0, 0.0, ph.GEMM_FP32, workspace=ws)
     ph.gemm(A, B, Cb, 0.25, 0.0, ph.GEMM_FP32)
     assert ph.device_status() == 0
     assert torch.equal(Cb, 0.25 * Ca)

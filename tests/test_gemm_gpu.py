@@ -25,24 +25,53 @@ def _to(dev, x, half=False):
 
 
 # ---------------------------------------------------------------- gemm_fp32 (FFMA)
+def _ws32(ph, dev, M, N, K, use):
+    """Workspace for the FFMA kernel's transposed copy of A (its faster form), or None (A read in place)."""
+    import torch
+    if not use:
+        return None
+    need = ph.gemm_workspace_bytes(ph.GEMM_FP32, ph.F32, M, N, K)
+    assert need >= 4 * M * K
+    return torch.empty((need,), dtype=torch.uint8, device=dev)
+
+
+@pytest.mark.parametrize("use_ws", [False, True])
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 384, 320), (96, 100, 64), (4, 4, 4), (130, 260, 36),
                                    (1024, 1024, 1024)])
-def test_gemm_fp32_matches_oracle(ph, oracle, dev, M, N, K):
+def test_gemm_fp32_matches_oracle(ph, oracle, dev, M, N, K, use_ws):
     a, b, c = _inputs(oracle, M, N, K)
     want = oracle.gemm_rows(a, b, c, 0.125, 1.5)
     A, B, C = _to(dev, a), _to(dev, b), _to(dev, c)
-    ph.gemm(A, B, C, 0.125, 1.5, ph.GEMM_FP32)
+    ph.gemm(A, B, C, 0.125, 1.5, ph.GEMM_FP32, workspace=_ws32(ph, dev, M, N, K, use_ws))
     assert ph.device_status() == 0
     assert oracle.rel_frobenius(C.cpu().numpy(), want) <= TOL_FP32
 
 
-def test_gemm_fp32_is_a_sequential_fma_chain(ph, oracle, dev):
+@pytest.mark.parametrize("M,N,K", [(130, 260, 36), (1000, 520, 4104), (2048, 1024, 272)])
+def test_gemm_fp32_both_forms_are_bit_identical(ph, oracle, dev, M, N, K):
+    """With workspace the kernel reads a transposed copy of A; the arithmetic per element is the same chain."""
+    import torch
+    a, b, c = _inputs(oracle, M, N, K)
+    A, B = _to(dev, a), _to(dev, b)
+    C0, C1 = _to(dev, c), _to(dev, c)
+    ph.gemm(A, B, C0, 0.75, -1.25, ph.GEMM_FP32)
+    ph.gemm(A, B, C1, 0.75, -1.25, ph.GEMM_FP32, workspace=_ws32(ph, dev, M, N, K, True))
+    assert ph.device_status() == 0
+    assert torch.equal(C0, C1)
+    # a workspace that is too small is not an error: the in-place form runs
+    C2 = _to(dev, c)
+    ph.gemm(A, B, C2, 0.75, -1.25, ph.GEMM_FP32, workspace=torch.empty((256,), dtype=torch.uint8, device=dev))
+    assert torch.equal(C0, C2)
+
+
+@pytest.mark.parametrize("use_ws", [False, True])
+def test_gemm_fp32_is_a_sequential_fma_chain(ph, oracle, dev, use_ws):
     """k ascending, one fma per step, then mul, mul, add: bit-identical to that chain in f32."""
     import torch
     M, N, K = 64, 64, 96
     a, b, c = _inputs(oracle, M, N, K)
     A, B, C = _to(dev, a), _to(dev, b), _to(dev, c)
-    ph.gemm(A, B, C, 0.125, 1.5, ph.GEMM_FP32)
+    ph.gemm(A, B, C, 0.125, 1.5, ph.GEMM_FP32, workspace=_ws32(ph, dev, M, N, K, use_ws))
     # exact emulation of fma.rn in f64: a*b is exact in f64, one rounding to f32 per step
     acc64 = np.zeros((M, N), dtype=np.float32)
     for k in range(K):
@@ -56,7 +85,8 @@ def test_gemm_fp32_is_a_sequential_fma_chain(ph, oracle, dev):
     assert np.allclose(got, want, rtol=1e-6, atol=1e-6)
 
 
-def test_gemm_fp32_exact_integer_case_with_guard(ph, dev):
+@pytest.mark.parametrize("use_ws", [False, True])
+def test_gemm_fp32_exact_integer_case_with_guard(ph, dev, use_ws):
     """The reference's masking example: A=(i%7)-3, B=(i%5)-2, 96x64x100, sentinel past the extent
     (phobos-bench/examples/masking.rs:109-152)."""
     import torch
@@ -67,14 +97,15 @@ def test_gemm_fp32_exact_integer_case_with_guard(ph, dev):
     buf = torch.full((M * N + GUARD,), SENT, device=dev)
     buf[:M * N] = 0.0
     C = buf[:M * N].view(M, N)
-    ph.gemm(_to(dev, a), _to(dev, b), C, 1.0, 0.0, ph.GEMM_FP32)
+    ph.gemm(_to(dev, a), _to(dev, b), C, 1.0, 0.0, ph.GEMM_FP32, workspace=_ws32(ph, dev, M, N, K, use_ws))
     assert ph.device_status() == 0
     out = buf.cpu().numpy()
     assert np.array_equal(out[:M * N].reshape(M, N), want)
     assert np.all(out[M * N:] == SENT), "store past the extent"
 
 
-def test_gemm_fp32_strided_views(ph, oracle, dev):
+@pytest.mark.parametrize("use_ws", [False, True])
+def test_gemm_fp32_strided_views(ph, oracle, dev, use_ws):
     """Row pitch larger than the row length (a region of a bigger tensor)."""
     M, N, K = 128, 192, 160
     big_a = oracle.lcg_fill(1, M * (K + 32)).reshape(M, K + 32)
@@ -82,7 +113,7 @@ def test_gemm_fp32_strided_views(ph, oracle, dev):
     big_c = oracle.lcg_fill(3, M * (N + 64)).reshape(M, N + 64)
     want = oracle.gemm_rows(big_a[:, :K], big_b[:, :N], big_c[:, :N], 2.0, -1.0)
     A, B, C = _to(dev, big_a), _to(dev, big_b), _to(dev, big_c)
-    ph.gemm(A[:, :K], B[:, :N], C[:, :N], 2.0, -1.0, ph.GEMM_FP32)
+    ph.gemm(A[:, :K], B[:, :N], C[:, :N], 2.0, -1.0, ph.GEMM_FP32, workspace=_ws32(ph, dev, M, N, K, use_ws))
     assert ph.device_status() == 0
     got = C.cpu().numpy()
     assert oracle.rel_frobenius(got[:, :N], want) <= TOL_FP32
