@@ -392,7 +392,9 @@ def bench_gemm(ctx: Ctx, name: str, M: int, N: int, K: int, alpha: float, beta: 
     flops = gemm_flops(M, N, K)
     out = {"workload": name, "M": M, "N": N, "K": K, "alpha": alpha, "beta": beta,
            "tflops": flops / (ms_total * 1e-3) / 1e12, "ms_per_step": ms_total, "ms_per_launch": ms_launch,
-           "ms_min": ms_min, "input_sets": nsets, "workspace_bytes": ws_bytes}
+           "ms_min": ms_min, "input_sets": nsets, "workspace_bytes": ws_bytes,
+           # with workspace the FFMA GEMM is two launches: A transposed into the workspace, then the kernel
+           "launches_per_step": 2 if (kind == ph.GEMM_FP32 and ws_bytes) else 1}
     info = ph.device_info(dev.index or 0)
     ach = flops / (ms_launch * 1e-3) / 1e12
     if kind == ph.GEMM_FP32:
@@ -460,7 +462,7 @@ def bench_flash(ctx: Ctx, BH: int, S: int, D: int, peaks, cpu_baseline=True, e2e
     flops = 4.0 * BH * S * S * D
     ach = flops / (ms_launch * 1e-3) / 1e12
     peak = peaks["bf16_tflops"]
-    out = {"workload": "flash_fp32" if f32_storage else "flash_fp16", "batch_heads": BH, "seq_len": S, "head_dim": D,
+    out = {"workload": "flash_fp32" if f32_storage else "flash_fp16", "launches_per_step": 4 if f32_storage else 1, "batch_heads": BH, "seq_len": S, "head_dim": D,
            "tflops": flops / (ms_total * 1e-3) / 1e12, "ms_per_step": ms_total, "ms_per_launch": ms_launch,
            "ms_min": ms_min, "exp_per_s": BH * S * S / (ms_launch * 1e-3),
            "roofline": {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
@@ -770,7 +772,8 @@ def bench_partitioned(ctx: Ctx, world: int, rank: int, MNK: int, alpha: float, b
            "e2e": {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
                    "h2d_bytes_per_step": world * (hA.numel() + hB.numel() + hC.numel()) * 4,
                    "d2h_bytes_per_step": world * hOut.numel() * 4},
-           "gpu_launches": (1 + len(plan.steps)) * ctx.steps * world}
+           # per step and rank: the init leaf, then for every K chunk the transposition of the A block and the FFMA kernel
+           "gpu_launches": (1 + 2 * len(plan.steps)) * ctx.steps * world}
     return out
 
 
@@ -1106,7 +1109,7 @@ def main():
             "config": {"workload": head_name, **{k: head[k] for k in head if k in ("M", "N", "K", "n", "alpha", "beta", "batch_heads", "seq_len", "head_dim")},
                        "l2": f"{head.get('input_sets', 1)} rotating input sets, working set larger than L2"},
             "roofline": head["roofline"], "cpu_baseline": head.get("cpu_baseline"), "e2e": head.get("e2e"),
-            "gpu_launches": args.steps, "parity": head.get("parity"), "same_box_bar": head.get("same_box_bar"),
+            "gpu_launches": args.steps * head.get("launches_per_step", 1), "parity": head.get("parity"), "same_box_bar": head.get("same_box_bar"),
             "clocks": sampler.summary(ctx.windows), "suite": suite, "targets": targets}
     if args.csv:
         write_csv(args.csv, results, args, ph.device_info(dev.index or 0))
