@@ -10,7 +10,7 @@
 // to a sequential f32 fma chain.
 //
 // Structure: CTA tile 128x128, K step 16, 128 threads, 8 rows x 16 columns of outputs per
-// thread in registers (128 accumulators as 64 packed pairs), two CTAs per SM.  A and B tiles
+// thread in registers (128 accumulators as 64 packed pairs), two or three CTAs per SM.  A and B tiles
 // of 16 k are staged by TMA into a ring of shared-memory stages; a `full` mbarrier per stage
 // signals arrival and an `empty` mbarrier (one arrival per warp) lets the refill proceed
 // without a CTA-wide barrier, so warps drift apart by up to a stage.  The multiply-adds are
@@ -74,8 +74,9 @@ __device__ __forceinline__ float2 unpack2(unsigned long long v) {
 }
 
 // AT: the A operand is the transposed copy [K][M] and its tile lands as [k][m].
+// (the [k][m] form fits three CTAs per SM at 168 registers: +1 %)
 template <bool AT>
-__global__ void __launch_bounds__(THREADS, 2)
+__global__ void __launch_bounds__(THREADS, AT ? 3 : 2)
 gemm_f32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, F32Params p) {
   extern __shared__ uint8_t smem_raw[];
   // rounded up to 1024 B as an offset into the array, so that the compiler still knows the address space
