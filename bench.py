@@ -793,7 +793,7 @@ kernel matmul(A: tensor<f32>[M, K], B: tensor<f32>[K, N], C: tensor<f32>[M, N], 
 """
 
 
-def bench_plan_driven(ctx: Ctx, world: int, MNK: int, alpha: float, beta: float, steps: int = 2):
+def bench_plan_driven(ctx: Ctx, world: int, MNK: int, alpha: float, beta: float, steps: int = 3, warm: int = 2):
     """The same partitioned matmul through the C ABI only (rank 0 drives it): job text -> phobos_plan_make
     (HomeLoadPeerFetch over `world` nodes, the reference's default supertiles) -> one executor per GPU, tensors
     resident in GPU 0's HBM (device:// storage), LOAD / FETCH / STORE as device and peer copies, leaves by entry
@@ -834,19 +834,20 @@ scalar beta = f32 {beta}
     pl = ph.plan(prog, job.dims, supers=supers, nodes=world, scalars=scalars, policy=ph.HOME_LOAD_PEER_FETCH)
     pl.validate()
     tensors = [(t.uri, t.dtype, t.shape, t.mode) for t in job.tensors]
-    # the executors live as long as a pod's would: the first (untimed) run also grows each one's workspace
+    # the executors live as long as a pod's would: the untimed runs also grow each one's workspace
     times, served = [], 0
     exs = [ph.Executor(n, n, arena) for n in range(world)]
     try:
-        for it in range(1 + steps):
+        for it in range(warm + steps):
             with torch.cuda.device(homes[2]):
                 fill_block(ph, C, 3, 0, 0, MNK)
             for home in homes:
                 torch.cuda.synchronize(home)
             before = sum(ex.served_bytes for ex in exs)
             ph.run_plan(pl, prog, tensors, exs)
-            if it > 0:
-                times.append(max(ex.last_run_ms for ex in exs))
+            if it >= warm:
+                per_node = [round(ex.last_run_ms, 3) for ex in exs]
+                times.append(max(per_node))
             served = sum(ex.served_bytes for ex in exs) - before
     finally:
         for ex in exs:
@@ -869,7 +870,7 @@ scalar beta = f32 {beta}
             "path": "job text -> phobos_plan_make (HomeLoadPeerFetch) -> one executor per GPU; A, B, C device-resident, "
                     "each whole on one GPU (" + ", ".join(str(h) for h in homes) + "); timed on the device per "
                     "executor, the longest counts",
-            "supertile": list(shape), "output_grid": list(grid), "supers": supers,
+            "run_ms": [round(t, 3) for t in times], "warmup_runs": warm, "per_node_ms_last_run": per_node, "supertile": list(shape), "output_grid": list(grid), "supers": supers,
             "predicted_ms": (ranked[0]["makespan_sec"] * 1e3) if ranked else None, "fetch_bytes_planned": pl.fetch_bytes,
             "fetch_bytes_served": served, "fetch_matches_plan": served == pl.fetch_bytes,
             "parity": {"rel_frobenius": err, "tol": 1e-5, "rows": int(rows.size), "ok": bool(err <= 1e-5)}}

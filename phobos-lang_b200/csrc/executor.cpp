@@ -10,8 +10,9 @@
 //     parked ALLOCs fail with "device arena exhausted" (engine.rs:752-775)
 //   - COMPUTE resolves the kernel id to an entry name, builds row-major tensor
 //     descriptors from the tile table (engine.rs:588-601) and enqueues the
-//     native kernel on one of four streams, completion by event
-//     (engine.rs:632-650, 655-687); Write / RMW tiles become resident then
+//     native kernel on the compute stream (the reference rotates kernels and copies over four
+//     streams; here copies rotate over three and leaves have one of their own), completion by
+//     event (engine.rs:632-650, 655-687); Write / RMW tiles become resident then
 //   - FETCH pulls a resident tile from a peer executor; on one box this is a
 //     device-to-device copy over NVLink (cudaMemcpyPeerAsync) where the
 //     reference stages through host memory and gRPC (engine.rs:511-540)
@@ -255,9 +256,13 @@ void retry_frees(PhExecutor* ex) {
   if (freed) retry_allocs(ex);
 }
 
+// Copies (LOAD, FETCH, STORE) rotate over streams 1..3; stream 0 belongs to the leaves, so that a
+// COMPUTE whose operands are resident never queues behind a transfer it does not depend on (seen in a
+// host-side timeline of the 16384^3 plan on four GPUs: init leaves of 30 us completing 3 ms late behind
+// 64 MB peer copies that shared their stream).
 cudaStream_t pick_stream(PhExecutor* ex) {
-  cudaStream_t s = ex->streams[ex->next_stream];
-  ex->next_stream = (ex->next_stream + 1) % 4;
+  cudaStream_t s = ex->streams[1 + ex->next_stream];
+  ex->next_stream = (ex->next_stream + 1) % 3;
   return s;
 }
 
@@ -464,8 +469,8 @@ void do_compute(PhExecutor* ex, uint64_t iid, const Node& n) {
     if (cudaMalloc(&ex->workspace, need) != cudaSuccess) return fail_instr(ex, iid, PH_ERR_DEVICE, "workspace allocation failed");
     ex->workspace_bytes = need;
   }
-  // kernels that use the shared workspace are serialised on stream 0
-  cudaStream_t s = need ? ex->streams[0] : pick_stream(ex);
+  // leaves run on stream 0 in issue order (those that use the shared workspace must not overlap anyway)
+  cudaStream_t s = ex->streams[0];
   int rc = phobos_launch(k->second.entry.c_str(), tensors.data(), (int32_t)tensors.size(), n.scalars.data(),
                          (int32_t)n.scalars.size(), n.in.grid, n.in.cta, hint, ex->workspace,
                          ex->workspace_bytes, s);
