@@ -144,21 +144,26 @@ def test_flash_fp16_b4_h32_s4096_d128(ph, oracle, dev):
     assert float((O2.float() - 2 * O.float()).abs().max()) <= 2.0 ** -23
 
 
-def test_matmul_cluster_fp32_16384_leaf_chain(ph, oracle, dev):
+@pytest.mark.parametrize("with_workspace", [False, True])
+def test_matmul_cluster_fp32_16384_leaf_chain(ph, oracle, dev, with_workspace):
     """One GPU's view of the partitioned matmul at the full size: the init leaf (C = beta*C) and a chain
     of step leaves (C = alpha*A_k@B_k + C) over K chunks of 2048, as the cluster plan issues them
-    (phobos-lang/src/clustergen.rs:1301-1399)."""
+    (phobos-lang/src/clustergen.rs:1301-1399).  With workspace the step leaf reads a transposed copy of
+    its A block (the faster form of the FFMA kernel)."""
     import torch
     M = N = K = 16384
     alpha, beta, kc = 0.125, 1.5, 2048
     A, B, C = _device_inputs(ph, torch, dev, M, N, K, torch.float32, torch.float32, 1.0)
+    ws = None
+    if with_workspace:
+        ws = torch.empty((ph.gemm_workspace_bytes(ph.GEMM_FP32, ph.F32, M, N, kc),), dtype=torch.uint8, device=dev)
     rows = _rows(M, 10, 15)
     idx = torch.from_numpy(rows.astype(np.int64)).to(dev)
     c0 = C.index_select(0, idx).cpu().numpy()
     ph.launch("matmul_init", [C], [ph.scalar_f32(1, beta)], grid=(1, 1, 1), cta=(256, 1, 1))
     for k0 in range(0, K, kc):
         ph.launch("matmul", [A[:, k0:k0 + kc], B[k0:k0 + kc, :], C], [ph.scalar_f32(3, alpha), ph.scalar_f32(4, beta)],
-                  grid=(1, 1, 1), cta=(256, 1, 1), kind_hint=ph.KIND_AUTO | ph.LAUNCH_STEP_LEAF)
+                  grid=(1, 1, 1), cta=(256, 1, 1), kind_hint=ph.KIND_AUTO | ph.LAUNCH_STEP_LEAF, workspace=ws)
     assert ph.device_status() == 0
     a = A.index_select(0, idx).cpu().numpy()
     want = oracle.gemm_rows(a, B.cpu().numpy(), c0, alpha, beta)
