@@ -94,8 +94,8 @@ gemm_f32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   // Tile of this CTA.  CTAs are dispatched in index order, about two per SM at a time, and the tiles in flight
   // walk K together, so an A or B k-slab fetched from DRAM by one of them is an L2 hit for the others that
   // share its row or column block.  DRAM traffic per "wave" is therefore (rows + columns of the block of tiles
-  // in flight) panels: bands of 16 tile rows, odd bands walked right to left, make that block about square
-  // (16 x 18 for 296 tiles in flight; bands of 8 read a third more).
+  // in flight) panels: bands of 16 tile rows, odd bands walked right to left, keep that block compact
+  // (16 x 18 for 296 tiles in flight, 16 x 28 for 444; bands of 8 read a third more).
   int mb, nb;
   {
     constexpr int GROUP = 16;
