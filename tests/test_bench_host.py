@@ -47,3 +47,22 @@ def test_reference_arm_prints_one_json_line():
     assert line["impl"] == "reference" and line["unit"] == "TFLOP/s" and line["value"] > 0
     assert line["config"]["workload"] == "gemm_fp16tc_fp32acc"
     assert line["cpu_baseline"]["kind"] == "port" and line["e2e"]["h2d_bytes_per_step"] == 0
+
+
+def test_traffic_provenance_hashes_code_not_wording():
+    """The figure of an ncu capture stays attached to a kernel while only its comments change, and is
+    reported stale as soon as the code does."""
+    bench = load_bench()
+    a = '// header\n__global__ void k(int* p) { /* note */ p[0] = 1;  // "x"\n  const char* s = "a // b";\n}\n'
+    b = '// another header, reworded\n__global__ void k(int* p) {\n  p[0] = 1;\n  const char* s = "a // b";\n}\n'
+    c = a.replace("p[0] = 1", "p[0] = 2")
+    d = a.replace('"a // b"', '"a / b"')
+    assert bench._code_only(a) == bench._code_only(b)
+    assert bench._code_only(a) != bench._code_only(c)
+    assert bench._code_only(a) != bench._code_only(d)      # string literals are code
+    # every entry of the committed table names a kernel source that exists and a profile that exists
+    table = json.loads((ROOT / "profiles" / "ncu_traffic.json").read_text())
+    for name, e in table.items():
+        assert name in bench.KERNEL_FILES
+        assert (ROOT / e["profile"]).exists()
+        assert e["kernel_sha"] == bench.kernel_sha(name), f"{name}: the capture is older than the kernel source"
