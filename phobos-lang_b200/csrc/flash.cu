@@ -76,6 +76,10 @@
 //    one; a block's buffer is held for softmax + 2400 clocks (P seen by the issuer, 8 MMAs, the
 //    commit seen by the other issuer, 8 MMAs, S seen), so three buffers give a period of
 //    (softmax + 2400) / 3 >= 1900 clocks per block, no better than the 1920 of this kernel.
+//  * The keys 64-127 of S(j+1) issued by a second thread per tile as soon as the softmax warps hold
+//    S(j) in registers (those columns carry no P), so that 8 + 8 half-width MMAs instead of 16 follow
+//    P: 1076 against 1135 on the same GPU; an N = 64 MMA occupies the pipe for ~57 clocks where an
+//    N = 128 one takes ~77, so two halves cost more than the whole.
 //  * The exponential loop on its own (register data, idle SM): 1180 clocks per 128 keys for one
 //    warp per scheduler, 1050 per block with two (the MUFU floor is 1024: 4096 ex2 per scheduler
 //    at 4 per clock); with 2/8 or 3/8 of the pairs as a cubic on the FMA/ALU pipes 1080 and 920:
